@@ -1,0 +1,232 @@
+/*
+ * llmqrt_b200 -- C ABI of the sm_100a kernels behind the quantized-linear and
+ * KV-cache-attention operators.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current device unless its name ends in `_host`;
+ *   - every call is asynchronous on `stream` and returns a status code at once; nothing is
+ *     allocated, freed or synchronised inside (the caller owns outputs and workspaces);
+ *   - matrices are row-major with an explicit leading dimension in ELEMENTS;
+ *   - weights are passed as W[N, K] row-major.  The reference hands the same memory to its
+ *     kernels as a "[K, N] column-major" view (stride [1, K]); the pointer is identical;
+ *   - 0 = success; negative = error, message available from llmqrt_last_error().
+ *
+ * Citations `ref:` give the reference interface (path inside the reference project) that the
+ * entry point stands in for.
+ */
+#ifndef LLMQRT_B200_H
+#define LLMQRT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* llmqrt_stream_t; /* a cudaStream_t */
+
+enum {
+  LLMQRT_OK = 0,
+  LLMQRT_ERR_INVALID = -1,     /* bad shape / alignment / dtype argument                  */
+  LLMQRT_ERR_CUDA = -2,        /* a CUDA runtime or driver call failed                    */
+  LLMQRT_ERR_WORKSPACE = -3,   /* workspace missing or too small                          */
+  LLMQRT_ERR_UNSUPPORTED = -4  /* valid request this build does not implement             */
+};
+
+enum { /* element types */
+  LLMQRT_F16 = 0,
+  LLMQRT_BF16 = 1,
+  LLMQRT_F32 = 2,
+  LLMQRT_E4M3 = 3,
+  LLMQRT_E5M2 = 4
+};
+
+/* Message of the last failing call made by this thread (never NULL). */
+const char* llmqrt_last_error(void);
+/* ABI version; bumped when a signature changes. */
+int llmqrt_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Workspace.  Kernels that split the reduction dimension across thread blocks keep partial
+ * sums and arrival counters in caller-provided scratch.  The scratch must be at least
+ * llmqrt_workspace_bytes() long, 256-byte aligned, ZERO-FILLED ONCE after allocation (kernels
+ * restore the counters to zero before they finish), and must not be shared by calls that can
+ * overlap on the GPU (use one per stream).
+ * ---------------------------------------------------------------------------------------- */
+size_t llmqrt_workspace_bytes(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Activation quantizers
+ * ---------------------------------------------------------------------------------------- */
+
+/* Dynamic symmetric int8 quantization of x[M, K] (fp16 / bf16).
+ * per_token != 0: one scale per row, else one scale for the whole tensor.
+ *   scale = clamp(absmax, 1e-5) / 127 evaluated in x's dtype, q = clamp(rint(x / scale)).
+ * Outputs: q int8 [M, K] (contiguous); scale_x in x's dtype ([M] or [1], may be NULL);
+ * scale_f32 ([M] or [1], may be NULL) = float(T(scale * scale_mul)) -- pass scale_mul = the
+ * weight scale to obtain the GEMM's alpha without a host round trip, or 1.0f.
+ * ref: runtime/nn_models/modules/linear/linear_sq.py:44-53 (per tensor), :55-65 (per token). */
+int llmqrt_quantize_int8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int per_token,
+                         int8_t* q, void* scale_x, float* scale_f32, float scale_mul, void* workspace,
+                         llmqrt_stream_t stream);
+
+/* Dynamic FP8 e4m3 quantization: scale = clamp(amax, 1e-12) / 448 in x's dtype,
+ * q = e4m3(clamp(x / scale, +-448)).  scale_f32 ([M] or [1]) = float(scale) * scale_mul.
+ * ref: runtime/nn_models/modules/linear/linear_fp8.py:11-32 (per tensor), :40-63 (per token). */
+int llmqrt_quantize_fp8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int per_token,
+                        uint8_t* q, float* scale_f32, float scale_mul, void* workspace, llmqrt_stream_t stream);
+
+/* Static FP8 quantization with a given one-element fp32 scale: q = e4m3(clamp(x / scale)).
+ * ref: runtime/nn_models/modules/linear/linear_fp8.py:34-37. */
+int llmqrt_quantize_fp8_static(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const float* scale,
+                               uint8_t* q, llmqrt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * W8A8 GEMMs.   acc[m, n] = sum_k a[m, k] * w[n, k]
+ * Requirements: K % 16 == 0, lda % 16 == 0, ldw % 16 == 0, 16-byte aligned a and w.
+ * `alpha_dev`, when not NULL, is a device fp32 scalar used instead of `alpha`.
+ * ---------------------------------------------------------------------------------------- */
+
+/* int8 x int8 -> exact int32 accumulators -> out fp16 = alpha * acc + beta * bias[n].
+ * bias is fp16 [N] and required, like the reference's.
+ * ref: w8a8_int8_linear_bbf16_obf16_per_tensor, runtime/csrc/smoothquant/sq_gemm.cu:36-160,
+ *      declared runtime/csrc/smoothquant/sq_gemm.h:12-17, bound runtime/csrc/bindings.cpp:10-11. */
+int llmqrt_w8a8_int8_linear_per_tensor(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, const void* bias,
+                                       float alpha, const float* alpha_dev, float beta, void* out, int64_t ldo,
+                                       int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+
+/* int8 GEMM with the per-token x per-output-channel dequantization fused:
+ * out = T( (float(acc) * w_scale[n]) * a_scale[m] + bias[n] ), T = out_dtype, bias optional.
+ * ref: w8a8_int8_linear_bbf16_obf16_per_channel, declared runtime/csrc/smoothquant/sq_gemm.h:19-24
+ *      (body commented out, sq_gemm.cu:162-278); arithmetic of
+ *      dequantize_activation_w_per_channel_a_per_token, runtime/utils/quantization_utils.py:90-97. */
+int llmqrt_w8a8_int8_linear_per_channel(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, const void* bias,
+                                        int bias_dtype, const float* a_scale, const float* w_scale, void* out,
+                                        int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
+                                        llmqrt_stream_t stream);
+
+/* Raw int32 accumulators acc[M, ldo] of the int8 GEMM (the quantity the parity gate checks bit for
+ * bit); same kernels as the two entry points above with the epilogue reduced to a store. */
+int llmqrt_w8a8_int8_gemm_s32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldo,
+                              int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+
+/* FP8 GEMM, tensor-wise scaling: out = T( alpha * acc_f32 + beta * bias[n] ), T in {bf16, fp16},
+ * bias optional and of type T.  a_format = LLMQRT_E4M3 or LLMQRT_E5M2; w is e4m3.
+ * ref: f8f8bf16_tensorwise (bound as cutlass_f8f8bf16_tensorwise_sm89),
+ *      runtime/csrc/fp8/sm89_fp8_tensorwise_cutlassgemm.cu:316-334, bindings.cpp:12. */
+int llmqrt_f8f8_tensorwise(const uint8_t* a, int a_format, int64_t lda, const uint8_t* w, int64_t ldw,
+                           const void* bias, float alpha, const float* alpha_dev, float beta, void* out, int out_dtype,
+                           int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+
+/* FP8 GEMM, row-wise scaling: out bf16 = ((acc_f32 * x_scale[m]) * w_scale[n]) + bias[n];
+ * bias optional, bf16 or fp32.
+ * ref: f8f8bf16_rowwise (bound as cutlass_f8f8bf16_rowwise_sm89),
+ *      runtime/csrc/fp8/sm89_fp8_rowwise_fbgemm.cu:582-606, bindings.cpp:13. */
+int llmqrt_f8f8bf16_rowwise(const uint8_t* a, int a_format, int64_t lda, const uint8_t* w, int64_t ldw,
+                            const void* bias, int bias_dtype, const float* x_scale, const float* w_scale, void* out,
+                            int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+
+/* Path selection of the W8A8 GEMMs, for tests and benchmarks: 0 = automatic (default),
+ * 1 = register-operand streaming kernel only, 2 = tcgen05/TMEM kernel only.  Process-wide. */
+int llmqrt_set_gemm_path(int path);
+
+/* ------------------------------------------------------------------------------------------
+ * AWQ W4A16
+ * Reference storage: qweight int32 [K, N/8] and qzeros int32 [K/G, N/8], eight 4-bit values per
+ * word along N with nibble i holding column 8j + {0,2,4,6,1,3,5,7}[i]; scales fp16 [K/G, N].
+ * ---------------------------------------------------------------------------------------- */
+
+/* W[K, N] fp16 = (nibble(qweight) - nibble(qzeros[k/G])) * scales[k/G].
+ * ref: awq_dequantize_triton, runtime/triton_kernels/awq_kernels.py:273-320 (kernel :33-127). */
+int llmqrt_awq_dequantize(const int32_t* qweight, const void* scales, const int32_t* qzeros, int64_t K, int64_t N,
+                          int64_t group_size, void* out, llmqrt_stream_t stream);
+
+/* One-time repack of a layer into the streaming layout the GEMM kernels read:
+ *   wq_t  uint32 [N, K/8]  eight K-consecutive values per word, value 2p in nibble p and 2p+1 in nibble p+4;
+ *   sz_t  half2  [N, K/G]  per (column, group): { scale, -(1024 + zero) } as two fp16.
+ * ref: replaces the per-call unpacking of runtime/triton_kernels/awq_kernels.py:205-250. */
+int llmqrt_awq_repack(const int32_t* qweight, const void* scales, const int32_t* qzeros, int64_t K, int64_t N,
+                      int64_t group_size, uint32_t* wq_t, uint32_t* sz_t, llmqrt_stream_t stream);
+
+/* C[M, N] fp16 = x[M, K] fp16 @ dequant(W) (+ bias fp16 [N], optional) on the repacked layer.
+ * fp32 accumulation; K % 128 == 0 when group_size < K, N % 8 == 0.
+ * ref: awq_gemm_triton, runtime/triton_kernels/awq_kernels.py:328-378 (kernel :134-267), and the
+ *      dequantize + matmul branch of runtime/nn_models/modules/linear/linear_awq.py:49-53. */
+int llmqrt_awq_gemm(const void* x, int64_t ldx, const uint32_t* wq_t, const uint32_t* sz_t, const void* bias,
+                    void* out, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t group_size, void* workspace,
+                    llmqrt_stream_t stream);
+
+/* Dequantize the repacked layer to W^T fp16 [N, K] (K contiguous), the operand layout of the
+ * tcgen05 fp16 GEMM used for large M. */
+int llmqrt_awq_dequantize_t(const uint32_t* wq_t, const uint32_t* sz_t, int64_t K, int64_t N, int64_t group_size,
+                            void* out, llmqrt_stream_t stream);
+
+/* Dense 16-bit GEMM on tcgen05: out[M, N] = a[M, K] @ w[N, K]^T (+ bias[n]), fp32 accumulate,
+ * a / w / out / bias all of type `dtype` (fp16 or bf16).  K % 8 == 0.
+ * ref: the torch.matmul of runtime/nn_models/modules/linear/linear_awq.py:53. */
+int llmqrt_gemm_16bit(const void* a, int64_t lda, const void* w, int64_t ldw, const void* bias, void* out,
+                      int64_t ldo, int dtype, int64_t M, int64_t N, int64_t K, void* workspace,
+                      llmqrt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Attention over the contiguous GQA KV cache.  dtype = fp16 or bf16 for q, k, v, caches, out.
+ * Query head h reads KV head h / (Hq / Hkv).  head_dim must be 64 or 128.
+ * ---------------------------------------------------------------------------------------- */
+
+/* cache[b, cache_seqlens[b] + s] = k/v[b, s] for s < S_new.  Caches are [Bc, Smax, Hkv, d] with the
+ * given batch and row strides (elements); k/v are [B, S_new, Hkv, d] contiguous.
+ * ref: the in-place append of flash_attn_with_kvcache (call site
+ *      runtime/nn_models/modules/nonlinear/attn.py:305-315) and WindowedCache.update_kv,
+ *      runtime/nn_models/modules/nonlinear/cache.py:41-46 (cache_seqlens == NULL: write at `start_pos`). */
+int llmqrt_kv_append(void* k_cache, void* v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
+                     const void* k, const void* v, const int32_t* cache_seqlens, int32_t start_pos, int dtype,
+                     int64_t B, int64_t S_new, int64_t Hkv, int64_t d, int64_t Smax, llmqrt_stream_t stream);
+
+/* Decode attention: q [B, Hq, d] (one new token per sequence) attends to cache rows
+ * [0, seqlens[b]) of sequence b; out [B, Hq, d].  softcap = 0 disables logit soft-capping.
+ * ref: flash_attn_with_kvcache call site, runtime/nn_models/modules/nonlinear/attn.py:300-315. */
+int llmqrt_attn_decode(const void* q, const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
+                       int64_t cache_row_stride, const int32_t* seqlens, void* out, int dtype, int64_t B, int64_t Hq,
+                       int64_t Hkv, int64_t d, int64_t max_seqlen, float softcap, void* workspace,
+                       llmqrt_stream_t stream);
+
+/* Prefill attention over the new tokens: q [B, S, Hq, d], k / v [B, S, Hkv, d], out [B, S, Hq, d],
+ * token stride given in elements (heads and d contiguous), causal mask optional.
+ * ref: flash_attn_func call site, runtime/nn_models/modules/nonlinear/attn.py:283-298. */
+int llmqrt_attn_prefill(const void* q, int64_t q_token_stride, const void* k, const void* v, int64_t kv_token_stride,
+                        void* out, int64_t out_token_stride, int dtype, int64_t B, int64_t S, int64_t Hq, int64_t Hkv,
+                        int64_t d, int causal, float softcap, llmqrt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Block glue used by the decode step (each fuses what the reference runs as a chain of torch ops)
+ * ---------------------------------------------------------------------------------------- */
+
+/* y = weight * T(x32 * rsqrt(mean(x32^2) + eps)); optional residual: x <- x + residual first
+ * (the sum is written back to `x_out` when not NULL).  Optional fused per-token int8 quantization
+ * of y (q, scale_f32 not NULL), same arithmetic as llmqrt_quantize_int8.
+ * ref: RMSNorm.forward, runtime/nn_models/modules/nonlinear/norm.py:10-16; residual adds of
+ *      LlamaLikeBlock.forward, runtime/nn_models/modules/nonlinear/block.py:64-78. */
+int llmqrt_rmsnorm(const void* x, const void* residual, void* x_out, const void* weight, float eps, void* y,
+                   int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H, llmqrt_stream_t stream);
+
+/* Rotary embedding (half-split pairing) of q [B, S, Hq, d] and k [B, S, Hkv, d] in place at positions
+ * pos0 + s (pos_dev, when not NULL, is a device int32 scalar overriding pos0), then writes k and v
+ * [B, S, Hkv, d] into the caches at rows pos + s.  Angles are computed from `theta` in fp32.
+ * ref: RoPE.forward, runtime/nn_models/modules/nonlinear/attn.py:53-87, and cache.py:41-46. */
+int llmqrt_rope_kv_write(void* q, int64_t q_token_stride, void* k, const void* v, int64_t kv_token_stride,
+                         void* k_cache, void* v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
+                         int32_t pos0, const int32_t* pos_dev, float theta, int dtype, int64_t B, int64_t S,
+                         int64_t Hq, int64_t Hkv, int64_t d, llmqrt_stream_t stream);
+
+/* h = silu(gate) * up for gate_up [M, 2*I] (gate in columns [0, I), up in [I, 2I)), written to `y`
+ * [M, I] when not NULL, with optional fused per-token int8 quantization of h.
+ * ref: the activation of the Hugging Face Qwen2MLP, down_proj(act_fn(gate_proj(x)) * up_proj(x)),
+ *      which the reference passes through unchanged (mlp=module.mlp, runtime/nn_models/models/qwen2.py:153). */
+int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M,
+                    int64_t I, llmqrt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMQRT_B200_H */

@@ -1,0 +1,45 @@
+// Process-wide pieces of the C ABI: error buffer, version, workspace size, device properties.
+#include "common.cuh"
+
+namespace llmqrt {
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    cudaDeviceProp p;
+    if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) return 148;
+    cached = p.multiProcessorCount;
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+}  // namespace llmqrt
+
+extern "C" {
+
+const char* llmqrt_last_error(void) { return llmqrt::last_error_buffer(); }
+
+int llmqrt_abi_version(void) { return 1; }
+
+// 64 KiB of arrival counters followed by 160 MiB of partial sums.  Every kernel that splits its
+// reduction clamps the number of slices so that its partials fit (8 slices of a 64 x 18944 fp32
+// tile are 39 MiB).
+size_t llmqrt_workspace_bytes(void) { return llmqrt::LLMQRT_WS_COUNTER_BYTES + llmqrt::LLMQRT_WS_PARTIAL_BYTES; }
+
+}  // extern "C"
