@@ -211,13 +211,17 @@ int llmqrt_rmsnorm(const void* x, const void* residual, void* x_out, const void*
                    int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H, llmqrt_stream_t stream);
 
 /* Rotary embedding (half-split pairing) of q [B, S, Hq, d] and k [B, S, Hkv, d] in place at positions
- * pos0 + s (pos_dev, when not NULL, is a device int32 scalar overriding pos0), then writes k and v
- * [B, S, Hkv, d] into the caches at rows pos + s.  Angles are computed from `theta` in fp32.
- * ref: RoPE.forward, runtime/nn_models/modules/nonlinear/attn.py:53-87, and cache.py:41-46. */
+ * pos0 + s (pos_dev, when not NULL, is a device int32 scalar overriding pos0), then, when k_cache is
+ * not NULL, writes the rotated k and v [B, S, Hkv, d] into the caches at rows pos + s.
+ * cos_table / sin_table are fp32 [table_rows, d/2] (angle = pos * theta^(-2i/d), the real and
+ * imaginary parts of the reference's freqs_cis); tokens whose position is outside the table are left
+ * untouched.
+ * ref: RoPE.forward, runtime/nn_models/modules/nonlinear/attn.py:53-87 (table :37-43), cache.py:41-46. */
 int llmqrt_rope_kv_write(void* q, int64_t q_token_stride, void* k, const void* v, int64_t kv_token_stride,
                          void* k_cache, void* v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
-                         int32_t pos0, const int32_t* pos_dev, float theta, int dtype, int64_t B, int64_t S,
-                         int64_t Hq, int64_t Hkv, int64_t d, llmqrt_stream_t stream);
+                         int32_t pos0, const int32_t* pos_dev, const float* cos_table, const float* sin_table,
+                         int64_t table_rows, int dtype, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t d,
+                         llmqrt_stream_t stream);
 
 /* h = silu(gate) * up for gate_up [M, 2*I] (gate in columns [0, I), up in [I, 2I)), written to `y`
  * [M, I] when not NULL, with optional fused per-token int8 quantization of h.

@@ -1,0 +1,127 @@
+"""Attention entry points with the call signatures the reference uses from the flash-attn package.
+
+`flash_attn_func` and `flash_attn_with_kvcache` accept the keyword subset of the reference's two
+call sites (runtime/nn_models/modules/nonlinear/attn.py:290-298 and :305-315) and run this
+package's own sm_100a kernels; arguments of the flash-attn API that the reference never sets are
+accepted only at their neutral values.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib as L
+
+
+def _check_common(q, softmax_scale, dropout_p=0.0, window_size=(-1, -1), alibi_slopes=None):
+    if dropout_p != 0.0:
+        raise NotImplementedError("llmqrt_b200 attention: dropout is not supported (inference only)")
+    if alibi_slopes is not None:
+        raise NotImplementedError("llmqrt_b200 attention: ALiBi is not supported")
+    if tuple(window_size) != (-1, -1):
+        raise NotImplementedError("llmqrt_b200 attention: sliding windows are not supported")
+    d = q.shape[-1]
+    if softmax_scale is not None and not math.isclose(softmax_scale, d ** -0.5, rel_tol=1e-6):
+        raise NotImplementedError("llmqrt_b200 attention: only the default softmax scale d**-0.5 is supported")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("llmqrt_b200 attention: q/k/v must be fp16 or bf16")
+
+
+def _token_strided(x: torch.Tensor) -> torch.Tensor:
+    """[B, S, H, d] with heads and d contiguous and batches back to back; copies only if it must."""
+    B, S, H, d = x.shape
+    if x.stride(3) == 1 and x.stride(2) == d and x.stride(0) == S * x.stride(1) and x.stride(1) % 8 == 0 \
+            and x.data_ptr() % 16 == 0:
+        return x
+    return x.contiguous()
+
+
+def flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0,
+                    alibi_slopes=None, deterministic=False, return_attn_probs=False):
+    """O = softmax(mask(Q K^T / sqrt(d))) V.  q [B,S,Hq,d]; k, v [B,S,Hkv,d]; returns [B,S,Hq,d]."""
+    _check_common(q, softmax_scale, dropout_p, window_size, alibi_slopes)
+    if return_attn_probs:
+        raise NotImplementedError("llmqrt_b200 attention: attention probabilities are never materialised")
+    dev = L.require_cuda(q, k, v)
+    B, S, Hq, d = q.shape
+    if k.shape[1] != S or v.shape != k.shape or k.shape[0] != B or k.shape[3] != d:
+        raise RuntimeError("flash_attn_func: q, k, v must share batch, sequence length and head_dim")
+    Hkv = k.shape[2]
+    q, k, v = _token_strided(q), _token_strided(k), _token_strided(v)
+    if k.stride(1) != v.stride(1):
+        v = v.contiguous()
+        k = k.contiguous()
+    out = torch.empty((B, S, Hq, d), dtype=q.dtype, device=dev)
+    with torch.cuda.device(dev):
+        L.call("llmqrt_attn_prefill", L.ptr(q), q.stride(1), L.ptr(k), L.ptr(v), k.stride(1), L.ptr(out),
+               out.stride(1), L.dtype_code(q.dtype), B, S, Hq, Hkv, d, int(bool(causal)), float(softcap),
+               L.stream(dev))
+    return out
+
+
+def kv_append(k_cache, v_cache, k, v, cache_seqlens=None, start_pos: int = 0):
+    """cache[b, pos_b + s] = k/v[b, s] with pos_b = cache_seqlens[b] (device int32) or `start_pos`."""
+    dev = L.require_cuda(k_cache, v_cache, k, v, cache_seqlens)
+    B, S_new, Hkv, d = k.shape
+    if k_cache.stride(3) != 1 or k_cache.stride(2) != d or v_cache.stride() != k_cache.stride():
+        raise RuntimeError("kv_append: caches must be [B, S, Hkv, d] with heads and d contiguous")
+    with torch.cuda.device(dev):
+        L.call("llmqrt_kv_append", L.ptr(k_cache), L.ptr(v_cache), k_cache.stride(0), k_cache.stride(1),
+               L.ptr(k.contiguous()), L.ptr(v.contiguous()), L.ptr(cache_seqlens), int(start_pos),
+               L.dtype_code(k_cache.dtype), B, S_new, Hkv, d, k_cache.shape[1], L.stream(dev))
+
+
+def attn_decode(q, k_cache, v_cache, seqlens, max_seqlen: int, softcap: float = 0.0):
+    """q [B, Hq, d] attends to rows [0, seqlens[b]) of the caches [Bc, Smax, Hkv, d]; returns [B, Hq, d]."""
+    dev = L.require_cuda(q, k_cache, v_cache, seqlens)
+    B, Hq, d = q.shape
+    Hkv = k_cache.shape[2]
+    if k_cache.stride(3) != 1 or k_cache.stride(2) != d or v_cache.stride() != k_cache.stride():
+        raise RuntimeError("attn_decode: caches must be [B, S, Hkv, d] with heads and d contiguous")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise TypeError("attn_decode: q and the caches must share one dtype")
+    if seqlens.dtype != torch.int32:
+        raise TypeError("attn_decode: seqlens must be int32")
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    with torch.cuda.device(dev):
+        L.call("llmqrt_attn_decode", L.ptr(q), L.ptr(k_cache), L.ptr(v_cache), k_cache.stride(0), k_cache.stride(1),
+               L.ptr(seqlens), L.ptr(out), L.dtype_code(q.dtype), B, Hq, Hkv, d, int(max_seqlen), float(softcap),
+               L.ptr(L.workspace(dev)), L.stream(dev))
+    return out
+
+
+def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None, rotary_sin=None,
+                            cache_seqlens=None, cache_batch_idx=None, block_table=None, softmax_scale=None,
+                            causal=False, window_size=(-1, -1), softcap=0.0, rotary_interleaved=True,
+                            alibi_slopes=None, num_splits=0, max_seqlen_k=None):
+    """Decode step over the KV cache.
+
+    If k / v are given they are first written in place into the caches at row cache_seqlens[b];
+    attention then covers rows [0, cache_seqlens[b] + k.shape[1]).  q is [B, 1, Hq, d] (one new token per
+    sequence); the causal flag is immaterial for a single query.  `max_seqlen_k` (an addition to the
+    flash-attn signature) bounds the longest sequence after the append so that the split-KV grid can be
+    sized without reading cache_seqlens back; it defaults to the cache capacity.
+    """
+    _check_common(q, softmax_scale, 0.0, window_size, alibi_slopes)
+    if rotary_cos is not None or rotary_sin is not None or cache_batch_idx is not None or block_table is not None:
+        raise NotImplementedError("llmqrt_b200 attention: rotary-in-kernel, batch indirection and paged caches are not supported")
+    B, Sq, Hq, d = q.shape
+    if Sq != 1:
+        raise NotImplementedError("flash_attn_with_kvcache: one query token per sequence (use flash_attn_func for prefill)")
+    dev = L.require_cuda(q, k_cache, v_cache, k, v)
+    if cache_seqlens is None:
+        raise RuntimeError("flash_attn_with_kvcache: cache_seqlens is required")
+    if isinstance(cache_seqlens, int):
+        cache_seqlens = torch.full((B,), cache_seqlens, dtype=torch.int32, device=dev)
+    seqlens = cache_seqlens
+    if k is not None:
+        if v is None:
+            raise RuntimeError("flash_attn_with_kvcache: k and v must be given together")
+        kv_append(k_cache, v_cache, k.to(k_cache.dtype), v.to(v_cache.dtype), cache_seqlens=cache_seqlens)
+        seqlens = cache_seqlens + k.shape[1]
+    cap = k_cache.shape[1]
+    out = attn_decode(q.reshape(B, Hq, d), k_cache, v_cache, seqlens,
+                      min(cap, max_seqlen_k) if max_seqlen_k is not None else cap, softcap)
+    return out.reshape(B, 1, Hq, d)

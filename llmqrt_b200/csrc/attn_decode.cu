@@ -1,0 +1,335 @@
+// Decode attention over the contiguous GQA KV cache (one query token per sequence), split-KV.
+//
+// HBM-bound: every K and V row of every sequence is read exactly once, HBM -> registers with
+// 128-bit loads, and consumed by warp-level MMAs whose 16-row operand is the group of query heads
+// that share the KV head (GQA packing: up to 8 query heads per pass), so the arithmetic stays far
+// below the memory time.  No shared-memory staging of K/V:
+//   S = Q K^T : the K fragment of lane (g, t) is 16 contiguous bytes of key row g -- exactly what a
+//               coalesced load delivers; Q is pre-loaded with the same head_dim permutation.
+//   O += P V  : the V fragment needs two keys per register; two 16-byte loads (keys 2t, 2t+1) are
+//               interleaved with one byte-permute per register.  The MMA's n index is mapped to
+//               head_dim so that every load is a contiguous 128-byte row segment.
+// Grid (splits, Hkv, B); each block walks `chunk` keys with 4 warps (16 keys per warp step), merges
+// its warps through shared memory and writes either the final output (single split) or an
+// unnormalised partial (max, sum, O) that a small combine kernel reduces.
+#include "common.cuh"
+
+namespace llmqrt {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+template <bool BF16, int D>
+__global__ void __launch_bounds__(kThreads)
+attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
+                   const uint16_t* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
+                   const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int Hkv, int chunk,
+                   int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
+  constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int rep = Hq / Hkv;
+  const int L = seqlens[b];
+  const int key_begin = split * chunk;
+  if (key_begin >= L && !(L == 0 && split == 0)) return;
+  const int key_end = min(L, key_begin + chunk);
+  const int n_splits = L == 0 ? 1 : (L + chunk - 1) / chunk;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+  // ---- Q fragments: head row g (zero when g >= rep), same chunk order as the K loads ----
+  uint32_t qf[NJ][4];
+  {
+    const uint16_t* qrow = q + ((int64_t)b * Hq + hkv * rep + g) * D;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (g < rep) v = *reinterpret_cast<const uint4*>(qrow + 8 * (4 * j + t));
+      qf[j][0] = v.x; qf[j][1] = v.y; qf[j][2] = v.z; qf[j][3] = v.w;
+    }
+  }
+
+  float o[NH][8][4];
+#pragma unroll
+  for (int h = 0; h < NH; ++h)
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[h][e][c] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;      // row g: running max (log2 domain) and this lane's partial sum
+
+  const uint16_t* kb = k_cache + (int64_t)b * cache_batch_stride + (int64_t)hkv * D;
+  const uint16_t* vb = v_cache + (int64_t)b * cache_batch_stride + (int64_t)hkv * D;
+  const float sl2 = scale * kLog2e;
+
+  for (int key0 = key_begin + warp * 16; key0 < key_end; key0 += kWarps * 16) {
+    // ---- issue all loads of this step ----
+    uint4 kf[2][NJ];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      const int key = min(key0 + 8 * nb + g, key_end - 1);       // clamped rows are masked below
+      const uint16_t* kr = kb + (int64_t)key * cache_row_stride;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) kf[nb][j] = ldg_stream_16B(kr + 8 * (4 * j + t));
+    }
+    uint4 vf[4][NH];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int key = min(key0 + 2 * t + (s & 1) + 8 * (s >> 1), key_end - 1);
+      const uint16_t* vr = vb + (int64_t)key * cache_row_stride;
+#pragma unroll
+      for (int h = 0; h < NH; ++h) vf[s][h] = ldg_stream_16B(vr + 8 * (g + 8 * h));
+    }
+
+    // ---- S = Q K^T for 16 keys ----
+    float s_acc[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s_acc[nb][c] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        mma_16816<BF16>(s_acc[nb], qf[j][0], 0u, qf[j][1], 0u, kf[nb][j].x, kf[nb][j].y);
+        mma_16816<BF16>(s_acc[nb], qf[j][2], 0u, qf[j][3], 0u, kf[nb][j].z, kf[nb][j].w);
+      }
+    }
+
+    // ---- online softmax for head row g (this lane: keys 8nb + 2t, 8nb + 2t + 1) ----
+    float p[2][2];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float s = s_acc[nb][c];
+        if (softcap != 0.f) s = softcap * tanhf(s * scale / softcap) * kLog2e;
+        else s *= sl2;
+        if (key0 + 8 * nb + 2 * t + c >= key_end) s = -INFINITY;
+        p[nb][c] = s;
+        mx = fmaxf(mx, s);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);                        // finite: key0 < key_end
+    const float corr = exp2f(m_run - m_new);
+    m_run = m_new;
+    float psum = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        p[nb][c] = exp2f(p[nb][c] - m_new);
+        psum += p[nb][c];
+      }
+    l_run = l_run * corr + psum;
+#pragma unroll
+    for (int h = 0; h < NH; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        o[h][e][0] *= corr;
+        o[h][e][1] *= corr;
+      }
+    const uint32_t pa0 = pack2<BF16>(p[0][0], p[0][1]);          // key slots 2t, 2t+1
+    const uint32_t pa2 = pack2<BF16>(p[1][0], p[1][1]);          // key slots 2t+8, 2t+9
+
+    // ---- O += P V ----
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+      const uint32_t* v0 = &vf[0][h].x;
+      const uint32_t* v1 = &vf[1][h].x;
+      const uint32_t* v2 = &vf[2][h].x;
+      const uint32_t* v3 = &vf[3][h].x;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b0 = __byte_perm(v0[e >> 1], v1[e >> 1], sel);
+        const uint32_t b1 = __byte_perm(v2[e >> 1], v3[e >> 1], sel);
+        mma_16816<BF16>(o[h][e], pa0, 0u, pa2, 0u, b0, b1);
+      }
+    }
+  }
+
+  // ---- merge the warps of this block ----
+  __shared__ float sm_o[kWarps][8][D];
+  __shared__ float sm_m[kWarps][8];
+  __shared__ float sm_l[kWarps][8];
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (t == 0) {
+    sm_m[warp][g] = m_run;
+    sm_l[warp][g] = l_run;
+  }
+#pragma unroll
+  for (int h = 0; h < NH; ++h)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      sm_o[warp][g][8 * (2 * t + 8 * h) + e] = o[h][e][0];
+      sm_o[warp][g][8 * (2 * t + 1 + 8 * h) + e] = o[h][e][1];
+    }
+  __syncthreads();
+
+  for (int i = tid; i < rep * D; i += kThreads) {
+    const int hd = i / D, dd = i - hd * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, sm_m[w][hd]);
+    float lsum = 0.f, osum = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float f = exp2f(sm_m[w][hd] - M);
+        lsum += sm_l[w][hd] * f;
+        osum += sm_o[w][hd][dd] * f;
+      }
+    }
+    const int hq = hkv * rep + hd;
+    if (n_splits == 1) {
+      const float r = lsum > 0.f ? osum / lsum : 0.f;
+      uint16_t bits;
+      if constexpr (BF16) { __nv_bfloat16 hv = __float2bfloat16_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
+      else { __half hv = __float2half_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
+      out[((int64_t)b * Hq + hq) * D + dd] = bits;
+    } else {
+      const int64_t slot = ((int64_t)b * Hq + hq) * max_splits + split;
+      part_o[slot * D + dd] = osum;
+      if (dd == 0) {
+        part_ml[slot * 2] = M;
+        part_ml[slot * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+template <bool BF16, int D>
+__global__ void __launch_bounds__(D)
+attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int chunk,
+                           int max_splits, const float* __restrict__ part_o, const float* __restrict__ part_ml) {
+  const int hq = blockIdx.x, b = blockIdx.y, dd = threadIdx.x;
+  const int L = seqlens[b];
+  const int n_splits = (L + chunk - 1) / chunk;
+  if (n_splits <= 1) return;                       // the main kernel already wrote the result
+  const int64_t base = ((int64_t)b * Hq + hq) * max_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float lsum = 0.f, osum = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float f = exp2f(part_ml[(base + s) * 2] - M);
+    lsum += part_ml[(base + s) * 2 + 1] * f;
+    osum += part_o[(base + s) * D + dd] * f;
+  }
+  const float r = lsum > 0.f ? osum / lsum : 0.f;
+  uint16_t bits;
+  if constexpr (BF16) { __nv_bfloat16 hv = __float2bfloat16_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
+  else { __half hv = __float2half_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
+  out[((int64_t)b * Hq + hq) * D + dd] = bits;
+}
+
+__global__ void kv_append_kernel(uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, int64_t batch_stride16,
+                                 int64_t row_stride16, const uint4* __restrict__ k, const uint4* __restrict__ v,
+                                 const int32_t* __restrict__ seqlens, int start_pos, int S_new, int row16, int Smax) {
+  // one block per (b, s); row16 = Hkv * d / 8 sixteen-byte units per token
+  const int s = blockIdx.x, b = blockIdx.y;
+  const int pos = (seqlens ? seqlens[b] : start_pos) + s;
+  if (pos < 0 || pos >= Smax) return;              // never write outside the cache
+  const int64_t src = ((int64_t)b * S_new + s) * row16;
+  const int64_t dst = (int64_t)b * batch_stride16 + (int64_t)pos * row_stride16;
+  for (int i = threadIdx.x; i < row16; i += blockDim.x) {
+    k_cache[dst + i] = k[src + i];
+    v_cache[dst + i] = v[src + i];
+  }
+}
+
+template <bool BF16, int D>
+int launch_decode(const void* q, const void* kc, const void* vc, int64_t bs, int64_t rs, const int32_t* seqlens,
+                  void* out, int B, int Hq, int Hkv, int max_seqlen, float softcap, void* workspace, cudaStream_t st) {
+  // keys per block: 256, halved while the grid would not cover the SMs twice
+  int chunk = 256;
+  while (chunk > 64 && (int64_t)B * Hkv * ceil_div(max_seqlen, chunk) < 2 * sm_count()) chunk /= 2;
+  int max_splits = (int)ceil_div(max_seqlen > 0 ? max_seqlen : 1, chunk);
+  while (max_splits > 1 && (size_t)B * Hq * max_splits * (D + 2) * 4 > LLMQRT_WS_PARTIAL_BYTES) {
+    chunk *= 2;
+    max_splits = (int)ceil_div(max_seqlen, chunk);
+  }
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  if (max_splits > 1) {
+    if (!workspace) return set_error(LLMQRT_ERR_WORKSPACE, "attn_decode: split-KV needs the workspace");
+    part_o = reinterpret_cast<float*>(ws_partials(workspace));
+    part_ml = part_o + (size_t)B * Hq * max_splits * D;
+  }
+  const float scale = 1.0f / sqrtf((float)D);
+  attn_decode_kernel<BF16, D><<<dim3(max_splits, Hkv, B), kThreads, 0, st>>>(
+      reinterpret_cast<const uint16_t*>(q), reinterpret_cast<const uint16_t*>(kc),
+      reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out), Hq, Hkv, chunk,
+      max_splits, scale, softcap, part_o, part_ml);
+  if (int rc = check_launch("attn_decode")) return rc;
+  if (max_splits > 1) {
+    attn_decode_combine_kernel<BF16, D><<<dim3(Hq, B), D, 0, st>>>(seqlens, reinterpret_cast<uint16_t*>(out), Hq,
+                                                                    chunk, max_splits, part_o, part_ml);
+    return check_launch("attn_decode_combine");
+  }
+  return LLMQRT_OK;
+}
+
+}  // namespace
+}  // namespace llmqrt
+
+using namespace llmqrt;
+
+extern "C" {
+
+int llmqrt_kv_append(void* k_cache, void* v_cache, int64_t cache_batch_stride, int64_t cache_row_stride, const void* k,
+                     const void* v, const int32_t* cache_seqlens, int32_t start_pos, int dtype, int64_t B,
+                     int64_t S_new, int64_t Hkv, int64_t d, int64_t Smax, llmqrt_stream_t stream) {
+  LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "kv_append: dtype must be fp16 or bf16");
+  LLMQRT_REQUIRE(B >= 0 && S_new >= 0 && Hkv > 0 && d > 0 && (Hkv * d) % 8 == 0, "kv_append: bad shape");
+  LLMQRT_REQUIRE(cache_batch_stride % 8 == 0 && cache_row_stride % 8 == 0, "kv_append: strides must be multiples of 8");
+  if (B == 0 || S_new == 0) return LLMQRT_OK;
+  LLMQRT_REQUIRE(k_cache && v_cache && k && v, "kv_append: null pointer");
+  LLMQRT_REQUIRE(((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                   reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0,
+                 "kv_append: pointers must be 16-byte aligned");
+  const int row16 = (int)(Hkv * d / 8);
+  kv_append_kernel<<<dim3((unsigned)S_new, (unsigned)B), row16 < 256 ? row16 : 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<uint4*>(k_cache), reinterpret_cast<uint4*>(v_cache), cache_batch_stride / 8,
+      cache_row_stride / 8, reinterpret_cast<const uint4*>(k), reinterpret_cast<const uint4*>(v), cache_seqlens,
+      start_pos, (int)S_new, row16, (int)Smax);
+  return check_launch("kv_append");
+}
+
+int llmqrt_attn_decode(const void* q, const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
+                       int64_t cache_row_stride, const int32_t* seqlens, void* out, int dtype, int64_t B, int64_t Hq,
+                       int64_t Hkv, int64_t d, int64_t max_seqlen, float softcap, void* workspace,
+                       llmqrt_stream_t stream) {
+  LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "attn_decode: dtype must be fp16 or bf16");
+  LLMQRT_REQUIRE(d == 64 || d == 128, "attn_decode: head_dim must be 64 or 128 (got %lld)", (long long)d);
+  LLMQRT_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8, "attn_decode: need Hq %% Hkv == 0 and at most 8 query heads per KV head");
+  LLMQRT_REQUIRE(B >= 0 && B < 65536 && Hkv < 65536 && max_seqlen >= 0, "attn_decode: bad shape");
+  LLMQRT_REQUIRE(cache_batch_stride % 8 == 0 && cache_row_stride % 8 == 0, "attn_decode: cache strides must be multiples of 8");
+  if (B == 0) return LLMQRT_OK;
+  LLMQRT_REQUIRE(q && k_cache && v_cache && seqlens && out, "attn_decode: null pointer");
+  LLMQRT_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
+                   reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0, "attn_decode: pointers must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool bf = dtype == LLMQRT_BF16;
+#define LLMQRT_GO(BF, DD)                                                                                          \
+  return launch_decode<BF, DD>(q, k_cache, v_cache, cache_batch_stride, cache_row_stride, seqlens, out, (int)B,    \
+                               (int)Hq, (int)Hkv, (int)max_seqlen, softcap, workspace, st)
+  if (d == 128) { if (bf) LLMQRT_GO(true, 128); else LLMQRT_GO(false, 128); }
+  if (bf) LLMQRT_GO(true, 64); else LLMQRT_GO(false, 64);
+#undef LLMQRT_GO
+}
+
+}  // extern "C"

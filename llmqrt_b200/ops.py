@@ -152,3 +152,67 @@ def gemm_16bit(a, w, bias=None) -> torch.Tensor:
         L.call("llmqrt_gemm_16bit", L.ptr(a), a.stride(0), L.ptr(w), w.stride(0), L.ptr(bias), L.ptr(out), N,
                L.dtype_code(a.dtype), M, N, K, L.ptr(L.workspace(dev)), L.stream(dev))
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# AWQ W4A16
+# ---------------------------------------------------------------------------------------------
+# Above this many tokens the weights are dequantized once and multiplied by the tcgen05 fp16 GEMM;
+# at or below it the streaming dequant-GEMM reads the 4-bit weights directly.
+AWQ_STREAM_MAX_M = 64
+
+
+def awq_dequantize(qweight, scales, qzeros) -> torch.Tensor:
+    """W[K, N] in scales.dtype from the reference storage layout."""
+    dev = L.require_cuda(qweight, scales, qzeros)
+    K, N = qweight.shape[0], scales.shape[1]
+    G = K // scales.shape[0]
+    out = torch.empty((K, N), dtype=torch.float16, device=dev)
+    sc = scales if scales.dtype == torch.float16 else scales.to(torch.float16)
+    with torch.cuda.device(dev):
+        L.call("llmqrt_awq_dequantize", L.ptr(qweight.contiguous()), L.ptr(sc.contiguous()),
+               L.ptr(qzeros.contiguous()), K, N, G, L.ptr(out), L.stream(dev))
+    return out if scales.dtype == torch.float16 else out.to(scales.dtype)
+
+
+class AwqPacked:
+    """A layer repacked once into the K-major streaming layout (see llmqrt_awq_repack)."""
+
+    __slots__ = ("wq_t", "sz_t", "K", "N", "G")
+
+    def __init__(self, qweight, scales, qzeros):
+        dev = L.require_cuda(qweight, scales, qzeros)
+        self.K, self.N = int(qweight.shape[0]), int(scales.shape[1])
+        self.G = self.K // int(scales.shape[0])
+        self.wq_t = torch.empty((self.N, self.K // 8), dtype=torch.int32, device=dev)
+        self.sz_t = torch.empty((self.N, self.K // self.G), dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            L.call("llmqrt_awq_repack", L.ptr(qweight.contiguous()), L.ptr(scales.to(torch.float16).contiguous()),
+                   L.ptr(qzeros.contiguous()), self.K, self.N, self.G, L.ptr(self.wq_t), L.ptr(self.sz_t),
+                   L.stream(dev))
+
+
+def awq_dequantize_t(packed: AwqPacked) -> torch.Tensor:
+    """W^T[N, K] fp16 (K contiguous) from a repacked layer."""
+    dev = packed.wq_t.device
+    out = torch.empty((packed.N, packed.K), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        L.call("llmqrt_awq_dequantize_t", L.ptr(packed.wq_t), L.ptr(packed.sz_t), packed.K, packed.N, packed.G,
+               L.ptr(out), L.stream(dev))
+    return out
+
+
+def awq_gemm(x: torch.Tensor, packed: AwqPacked, bias=None) -> torch.Tensor:
+    """C[M, N] fp16 = x[M, K] fp16 @ dequant(W) (+ bias)."""
+    dev = L.require_cuda(x, packed.wq_t, bias)
+    x2 = _rows(x)
+    M, K = x2.shape
+    if K != packed.K:
+        raise RuntimeError(f"awq_gemm: x has K={K}, layer has K={packed.K}")
+    if M > AWQ_STREAM_MAX_M:
+        return gemm_16bit(x2, awq_dequantize_t(packed), bias)
+    out = torch.empty((M, packed.N), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        L.call("llmqrt_awq_gemm", L.ptr(x2), x2.stride(0), L.ptr(packed.wq_t), L.ptr(packed.sz_t), L.ptr(bias),
+               L.ptr(out), packed.N, M, packed.N, K, packed.G, L.ptr(L.workspace(dev)), L.stream(dev))
+    return out

@@ -1,0 +1,181 @@
+"""Parity of the attention and block-glue kernels against the CPU oracle and reference fixtures."""
+import pytest
+import torch
+
+from tests.util import bits_equal, load_golden, max_abs, ulp_mismatch_fraction
+
+pytestmark = pytest.mark.gpu
+
+ATTN_TOL = 2e-3       # max abs error allowed on attention outputs
+
+
+def _qkv(B, S, Hq, Hkv, d, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(B, S, Hq, d, generator=g).to(dtype), torch.randn(B, S, Hkv, d, generator=g).to(dtype),
+            torch.randn(B, S, Hkv, d, generator=g).to(dtype))
+
+
+# ------------------------------------------------------------------ prefill
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,S,Hq,Hkv,d", [(2, 64, 4, 2, 128), (1, 200, 14, 2, 64), (2, 129, 7, 1, 128),
+                                          (1, 1, 4, 4, 64), (1, 515, 28, 4, 128)])
+def test_prefill_causal(dtype, B, S, Hq, Hkv, d):
+    from llmqrt_b200.attention import flash_attn_func
+    from oracle import attention as oa
+    q, k, v = _qkv(B, S, Hq, Hkv, d, dtype, S + Hq)
+    out = flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=True)
+    ref = oa.attention_prefill(q, k, v, causal=True)
+    tol = ATTN_TOL if dtype == torch.float16 else 1.6e-2      # bf16 output has 8 mantissa bits
+    assert max_abs(out, ref) < tol
+
+
+def test_prefill_noncausal_softcap_and_strided_inputs():
+    from llmqrt_b200.attention import flash_attn_func
+    from oracle import attention as oa
+    B, S, Hq, Hkv, d = 2, 96, 8, 2, 64
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * d, generator=g).to(torch.float16)       # fused projection output
+    q = qkv[..., : Hq * d].reshape(B, S, Hq, d)
+    k = qkv[..., Hq * d: (Hq + Hkv) * d].reshape(B, S, Hkv, d)
+    v = qkv[..., (Hq + Hkv) * d:].reshape(B, S, Hkv, d)
+    qc, kc, vc = (t.cuda() for t in (qkv[..., : Hq * d], qkv[..., Hq * d: (Hq + Hkv) * d], qkv[..., (Hq + Hkv) * d:]))
+    qkv_c = qkv.cuda()
+    qv = qkv_c[..., : Hq * d].view(B, S, Hq, d)
+    kv = qkv_c[..., Hq * d: (Hq + Hkv) * d].view(B, S, Hkv, d)
+    vv = qkv_c[..., (Hq + Hkv) * d:].view(B, S, Hkv, d)
+    for causal, softcap in ((False, 0.0), (True, 30.0)):
+        out = flash_attn_func(qv, kv, vv, causal=causal, softcap=softcap)
+        ref = oa.attention_prefill(q, k, v, causal=causal, softcap=softcap)
+        assert max_abs(out, ref) < ATTN_TOL
+
+
+def test_prefill_full_size_properties():
+    # batch 4 x 2048 tokens, 28/4 heads, head_dim 128: row 0 of every head attends only to key 0
+    # (output == v[0]), and a causal run restricted to a prefix equals the prefix of the full run.
+    from llmqrt_b200.attention import flash_attn_func
+    B, S, Hq, Hkv, d = 4, 2048, 28, 4, 128
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(B, S, Hq, d, generator=g, device="cuda", dtype=torch.float16)
+    k = torch.randn(B, S, Hkv, d, generator=g, device="cuda", dtype=torch.float16)
+    v = torch.randn(B, S, Hkv, d, generator=g, device="cuda", dtype=torch.float16)
+    out = flash_attn_func(q, k, v, causal=True)
+    assert torch.isfinite(out.float()).all()
+    assert max_abs(out[:, 0], v[:, 0].repeat_interleave(Hq // Hkv, dim=1)) < 1e-3
+    part = flash_attn_func(q[:, :300].contiguous(), k[:, :300].contiguous(), v[:, :300].contiguous(), causal=True)
+    assert max_abs(out[:, :300], part) < 1e-3
+
+
+# ------------------------------------------------------------------ decode
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,Hq,Hkv,d,Smax,lens", [
+    (4, 28, 4, 128, 600, [1, 17, 300, 599]),
+    (3, 14, 2, 64, 260, [64, 255, 256]),
+    (2, 8, 1, 128, 128, [5, 127]),
+    (2, 4, 4, 64, 40, [0, 33]),
+])
+def test_decode_with_append(dtype, B, Hq, Hkv, d, Smax, lens):
+    from llmqrt_b200.attention import flash_attn_with_kvcache
+    from oracle import attention as oa
+    g = torch.Generator().manual_seed(B * Hq + d)
+    kc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype)
+    vc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype)
+    q = torch.randn(B, 1, Hq, d, generator=g).to(dtype)
+    kn = torch.randn(B, 1, Hkv, d, generator=g).to(dtype)
+    vn = torch.randn(B, 1, Hkv, d, generator=g).to(dtype)
+    seqlens = torch.tensor(lens, dtype=torch.int32)
+    kc_g, vc_g = kc.cuda(), vc.cuda()
+    out = flash_attn_with_kvcache(q.cuda(), kc_g, vc_g, k=kn.cuda(), v=vn.cuda(), cache_seqlens=seqlens.cuda(),
+                                  causal=True)
+    ref = oa.attention_decode_kvcache(q, kc, vc, kn, vn, seqlens)           # also appends into kc / vc
+    tol = ATTN_TOL if dtype == torch.float16 else 1.6e-2
+    assert max_abs(out, ref) < tol
+    assert bits_equal(kc_g.cpu(), kc) and bits_equal(vc_g.cpu(), vc)       # in-place append, nothing else touched
+
+
+def test_decode_config_shape_long_contexts():
+    # batch 32, 28/4 heads, head_dim 128, context lengths uniform in [512, 8192]; checked against the
+    # oracle on a subset of sequences (the oracle is O(L) per sequence and slow) and for finiteness on all
+    from llmqrt_b200.attention import attn_decode
+    from oracle import attention as oa
+    B, Hq, Hkv, d, Smax = 32, 28, 4, 128, 8192
+    g = torch.Generator(device="cuda").manual_seed(0)
+    kc = torch.randn(B, Smax, Hkv, d, generator=g, device="cuda", dtype=torch.float16)
+    vc = torch.randn(B, Smax, Hkv, d, generator=g, device="cuda", dtype=torch.float16)
+    q = torch.randn(B, Hq, d, generator=g, device="cuda", dtype=torch.float16)
+    lens = torch.randint(512, 8193, (B,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+    out = attn_decode(q, kc, vc, lens.cuda(), Smax)
+    assert torch.isfinite(out.float()).all()
+    for b in (0, 7, 31):
+        ref = oa.attention_decode_kvcache(q[b:b + 1].cpu().unsqueeze(1), kc[b:b + 1].cpu(), vc[b:b + 1].cpu(), None,
+                                          None, lens[b:b + 1])
+        assert max_abs(out[b], ref[0, 0]) < ATTN_TOL
+    out2 = attn_decode(q, kc, vc, lens.cuda(), Smax)
+    assert bits_equal(out, out2)                                            # fixed combine order: repeatable
+
+
+def test_decode_equals_last_row_of_prefill():
+    from llmqrt_b200.attention import attn_decode, flash_attn_func
+    B, S, Hq, Hkv, d = 2, 333, 28, 4, 128
+    q, k, v = (t.cuda() for t in _qkv(B, S, Hq, Hkv, d, torch.float16, 11))
+    full = flash_attn_func(q, k, v, causal=True)
+    lens = torch.full((B,), S, dtype=torch.int32, device="cuda")
+    dec = attn_decode(q[:, -1].contiguous(), k, v, lens, S)
+    assert max_abs(dec, full[:, -1]) < 1e-3
+
+
+# ------------------------------------------------------------------ glue
+@pytest.mark.parametrize("tag", ["f16", "bf16"])
+def test_rmsnorm_and_rope_match_reference_fixture(tag):
+    from llmqrt_b200 import glue
+    g = load_golden(f"glue_{tag}")
+    y, _, _, _ = glue.rmsnorm(g["norm_x"].cuda(), g["norm_w"].cuda(), 1e-6)
+    frac, dist = ulp_mismatch_fraction(y.cpu(), g["norm_y"])
+    assert dist <= 1 and frac < 0.02          # fp32 reduction order differs from torch's: at most 1 ulp
+    cos, sin = glue.rope_tables(64, 32, 1e6, "cuda")
+    q, k = g["rope_q"].cuda(), g["rope_k"].cuda()
+    kc = torch.zeros(2, 16, 2, 64, dtype=q.dtype, device="cuda")
+    vc = torch.zeros_like(kc)
+    v = g["cache_v_in"].to(q.dtype).cuda()
+    glue.rope_kv_write(q, k, v, cos, sin, pos0=5, k_cache=kc, v_cache=vc)
+    for got, want in ((q, g["rope_oq"]), (k, g["rope_ok"])):
+        frac, dist = ulp_mismatch_fraction(got.cpu(), want)
+        assert dist <= 1 and frac < 0.01      # fused multiply-add contraction of the complex product
+    assert bits_equal(kc[:, 5:8].cpu(), k.cpu()) and bits_equal(vc[:, 5:8].cpu(), v.cpu())
+    assert float(kc[:, :5].abs().max()) == 0 and float(kc[:, 8:].abs().max()) == 0
+    # position taken from a device scalar
+    q2, k2 = g["rope_q"].cuda(), g["rope_k"].cuda()
+    glue.rope_kv_write(q2, k2, None, cos, sin, pos0=0, pos_dev=torch.tensor([5], dtype=torch.int32, device="cuda"))
+    assert bits_equal(q2, q) and bits_equal(k2, k)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rmsnorm_residual_and_fused_quant(dtype):
+    from llmqrt_b200 import glue
+    from oracle import attention as oa
+    from oracle import quant as oq
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(5, 3584, generator=g).to(dtype)
+    r = torch.randn(5, 3584, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(3584, generator=g)).to(dtype)
+    y, h, q, s = glue.rmsnorm(x.cuda(), w.cuda(), 1e-6, residual=r.cuda(), quantize=True)
+    h_ref = x + r
+    assert bits_equal(h.cpu(), h_ref)
+    frac, dist = ulp_mismatch_fraction(y.cpu(), oa.rmsnorm(h_ref, w, 1e-6))
+    assert dist <= 1 and frac < 0.02
+    q_ref, s_ref = oq.quantize_int8(y.cpu(), per_token=True)              # quantizer applied to the kernel's own y
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.float().reshape(-1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_silu_mul_and_fused_quant(dtype):
+    from llmqrt_b200 import glue
+    from oracle import quant as oq
+    g = torch.Generator().manual_seed(2)
+    gu = torch.randn(6, 2 * 18944, generator=g).to(dtype)
+    h, q, s = glue.silu_mul(gu.cuda(), quantize=True)
+    gate, up = gu[:, :18944], gu[:, 18944:]
+    ref = torch.nn.functional.silu(gate) * up
+    frac, dist = ulp_mismatch_fraction(h.cpu(), ref)
+    assert dist <= 1 and frac < 0.01          # expf on the GPU vs the CPU's exp
+    q_ref, s_ref = oq.quantize_int8(h.cpu(), per_token=True)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.float().reshape(-1))
