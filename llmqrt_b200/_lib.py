@@ -115,12 +115,16 @@ def require_cuda(*tensors: torch.Tensor) -> torch.device:
 
 WORKSPACE_BYTES = int(_lib.llmqrt_workspace_bytes())
 _ws_lock = threading.Lock()
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_workspaces: dict[int, torch.Tensor] = {}
 
 
 def workspace(device: torch.device) -> torch.Tensor:
-    """Scratch buffer for the current stream of `device`: zero-filled once, then owned by the kernels."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), stream(device))
+    """Scratch buffer of `device`: zero-filled once, then owned by the kernels.
+
+    One buffer per device: calls of this package on the same device must be ordered (one stream, or
+    streams that depend on each other), because kernels that split their reduction share it.
+    """
+    key = device.index if device.index is not None else torch.cuda.current_device()
     ws = _workspaces.get(key)
     if ws is None:
         with _ws_lock:

@@ -238,7 +238,7 @@ extern "C" int llmqrt_attn_prefill(const void* q, int64_t q_token_stride, const 
 #define LLMQRT_RUN(BF, DD)                                                                                         \
   do {                                                                                                             \
     auto kern = attn_prefill_kernel<BF, DD>;                                                                       \
-    LLMQRT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));                 \
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;                \
     kern<<<grid, kThreads, smem, st>>>(reinterpret_cast<const uint16_t*>(q), q_token_stride,                       \
                                        reinterpret_cast<const uint16_t*>(k), reinterpret_cast<const uint16_t*>(v), \
                                        kv_token_stride, reinterpret_cast<uint16_t*>(out), out_token_stride, (int)S, \

@@ -246,7 +246,7 @@ int launch_gemm(const __half* X, int64_t ldx, const uint32_t* wq_t, const uint32
   }
   const size_t smem = (size_t)MB * 8 * xs_stride_bytes(kps);
   auto kern = awq_gemm_stream_kernel<MB>;
-  if (smem > 48 * 1024) LLMQRT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;
   kern<<<dim3(n_blocks, splits), kThreads, smem, st>>>(
       X, ldx, wq_t, sz_t, M, N, K, G, kps, splits,
       workspace ? reinterpret_cast<float*>(ws_partials(workspace)) : nullptr,

@@ -1,6 +1,10 @@
 // Process-wide pieces of the C ABI: error buffer, version, workspace size, device properties.
 #include "common.cuh"
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 namespace llmqrt {
 
 char* last_error_buffer() {
@@ -27,6 +31,21 @@ int sm_count() {
     cached_dev = dev;
   }
   return cached;
+}
+
+int ensure_dynamic_smem(const void* func, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> configured;
+  if (bytes <= 48 * 1024) return LLMQRT_OK;
+  int dev = 0;
+  LLMQRT_CUDA_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  int& have = configured[{dev, func}];
+  if (bytes > have) {
+    LLMQRT_CUDA_OK(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    have = bytes;
+  }
+  return LLMQRT_OK;
 }
 
 }  // namespace llmqrt

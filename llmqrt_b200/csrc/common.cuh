@@ -50,6 +50,10 @@ inline int* ws_counters(void* ws) { return reinterpret_cast<int*>(ws); }
 inline unsigned* ws_scalars(void* ws) { return reinterpret_cast<unsigned*>(ws) + LLMQRT_WS_NUM_COUNTERS; }
 inline void* ws_partials(void* ws) { return reinterpret_cast<char*>(ws) + LLMQRT_WS_COUNTER_BYTES; }
 int sm_count();  // cached multiprocessor count of the current device (capi.cu)
+// Raises the dynamic shared-memory limit of kernel `func` on the current device to at least `bytes`.
+// The attribute is only touched when a larger value than ever before is needed, so steady-state
+// launches (and stream capture after a warm-up call) make no driver call here.
+int ensure_dynamic_smem(const void* func, int bytes);
 
 // ----------------------------------------------------------------------------------------------
 // 16-bit float helpers.  T is __half or __nv_bfloat16.

@@ -172,7 +172,7 @@ int launch(const uint8_t* A, int64_t lda, const uint8_t* W, int64_t ldw, int M, 
   }
   const size_t smem = (size_t)MB * 8 * xs_stride_for(kps);
   auto kern = w8a8_stream_kernel<KIND, MB>;
-  if (smem > 48 * 1024) LLMQRT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;
   dim3 grid(n_blocks, splits);
   kern<<<grid, kThreads, smem, st>>>(A, lda, W, ldw, M, N, K, kps, splits,
                                      workspace ? ws_partials(workspace) : nullptr,

@@ -344,13 +344,7 @@ template <int KIND, int BN>
 int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const TcParams& prm, int grid, cudaStream_t st) {
   constexpr int smem = num_stages<BN>() * stage_bytes<BN>() + 1024;
   auto kern = gemm_tc_kernel<KIND, BN>;
-  static thread_local int configured_dev = -1;   // per instantiation and host thread
-  int dev = 0;
-  LLMQRT_CUDA_OK(cudaGetDevice(&dev));
-  if (configured_dev != dev) {
-    LLMQRT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured_dev = dev;
-  }
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
   kern<<<grid, kThreads, smem, st>>>(tm_p, tm_q, prm);
   return check_launch("gemm_tc");
 }

@@ -157,7 +157,7 @@ int llmqrt_rmsnorm(const void* x, const void* residual, void* x_out, const void*
   do {                                                                                                             \
     auto kern = rmsnorm_kernel<T>;                                                                                 \
     if (smem > 48 * 1024)                                                                                          \
-      LLMQRT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));          \
+      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;          \
     kern<<<(unsigned)M, kThreads, smem, st>>>(reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(residual), \
                                               reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), eps,  \
                                               reinterpret_cast<T*>(y), q, scale_f32, H);                            \
@@ -180,7 +180,7 @@ int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* 
   do {                                                                                                       \
     auto kern = silu_mul_kernel<T>;                                                                          \
     if (smem > 48 * 1024)                                                                                    \
-      LLMQRT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;    \
     kern<<<(unsigned)M, kThreads, smem, st>>>(reinterpret_cast<const T*>(gate_up), ld, reinterpret_cast<T*>(y), q, \
                                               scale_f32, I);                                                  \
   } while (0)

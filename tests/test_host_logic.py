@@ -1,0 +1,135 @@
+"""CPU-only tests: C-ABI exports, host-side tensor-parallel logic (gloo, world size 2), oracle TP emulation."""
+import os
+import re
+import subprocess
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    import ctypes
+    from llmqrt_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "llmqrt_b200.h")).read()
+    declared = set(re.findall(r"\b(llmqrt_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/llmqrt_b200.h but not exported"
+    assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
+    assert _lib._lib.llmqrt_abi_version() == 1
+    assert _lib.WORKSPACE_BYTES > 64 * 1024
+
+
+def test_product_path_refuses_cpu_tensors():
+    import pytest
+    from llmqrt_b200 import ops
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.int8_gemm_s32(torch.zeros(4, 16, dtype=torch.int8), torch.zeros(8, 16, dtype=torch.int8))
+
+
+def test_package_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "llmqrt_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith(".py"):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", src, re.M), f
+                assert "tests.golden" not in src and "_work/" not in src, f
+
+
+def test_head_assignment_partitions_heads():
+    from llmqrt_b200.tp import head_assignment
+    for hq, hkv in ((28, 4), (14, 2), (12, 2), (32, 8)):
+        rep = hq // hkv
+        for tp in (1, 2, 4, 8):
+            if not (hkv % tp == 0 or (tp % hkv == 0 and tp // hkv <= rep)):
+                continue
+            seen = []
+            for r in range(tp):
+                q, kv = head_assignment(hq, hkv, tp, r)
+                assert q and kv and all(h // rep in kv for h in q)          # every q head next to its KV head
+                assert len(q) % len(kv) == 0 and len(q) // len(kv) <= 8
+                seen += q
+            assert sorted(seen) == list(range(hq))                           # each query head exactly once
+    q, kv = head_assignment(28, 4, 8, 0)
+    assert (q, kv) == ([0, 1, 2, 3], [0])
+    q, kv = head_assignment(28, 4, 8, 1)
+    assert (q, kv) == ([4, 5, 6], [0])
+
+
+_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from llmqrt_b200.tp import allreduce_sum, greedy_select
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[2], rank=int(sys.argv[3]), world_size=2)
+rank = dist.get_rank()
+g = torch.Generator().manual_seed(7)
+logits = torch.randn(5, 64, generator=g)
+logits[0, 40] = logits[0, 3] = 9.0                      # tie across shards: lowest token id must win
+shard = logits[:, rank * 32:(rank + 1) * 32]
+val, idx = shard.max(dim=-1)
+tok = greedy_select(val, idx + rank * 32, 2)
+assert torch.equal(tok, logits.argmax(dim=-1)), (tok, logits.argmax(dim=-1))
+x = torch.full((3, 4), float(rank + 1))
+assert torch.equal(allreduce_sum(x, 2), torch.full((3, 4), 3.0))
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_greedy_select_and_allreduce_world_size_2_gloo(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    port = str(29600 + os.getpid() % 300)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+
+
+def test_oracle_tensor_parallel_emulation_matches_single_rank():
+    # Row-parallel partial sums with per-rank activation scales must stay close to the unsharded model.
+    from llmqrt_b200.tp import head_assignment, rows_of_heads
+    from oracle.qwen2 import Qwen2Oracle
+
+    class Cfg:
+        hidden, head_dim, rms_eps, rope_theta, dtype = 64, 16, 1e-6, 1e6, torch.bfloat16
+    Hq, Hkv, I, V, d = 4, 2, 96, 128, 16
+    g = torch.Generator().manual_seed(0)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=g) * 0.05).to(torch.bfloat16)
+
+    def quant(w):
+        s = (w.float().abs().amax(1, keepdim=True) / 127).clamp_min(1e-8)
+        return torch.round(w.float() / s).clamp(-128, 127).to(torch.int8), s.reshape(-1)
+
+    full = dict(wq=rnd(Hq * d, 64), wk=rnd(Hkv * d, 64), wv=rnd(Hkv * d, 64), bq=rnd(Hq * d), bk=rnd(Hkv * d),
+                bv=rnd(Hkv * d), wo=rnd(64, Hq * d), wg=rnd(I, 64), wu=rnd(I, 64), wd=rnd(64, I))
+    embed, lm_head = rnd(V, 64) * 10, rnd(V, 64)
+
+    def shards(tp):
+        out = []
+        for r in range(tp):
+            qh, kh = head_assignment(Hq, Hkv, tp, r)
+            qr, kr = rows_of_heads(qh, d), rows_of_heads(kh, d)
+            i0, i1 = r * I // tp, (r + 1) * I // tp
+            wqkv, sqkv = quant(torch.cat([full["wq"][qr], full["wk"][kr], full["wv"][kr]]))
+            wo, so = quant(full["wo"][:, qr])
+            wgu, sgu = quant(torch.cat([full["wg"][i0:i1], full["wu"][i0:i1]]))
+            wd, sd = quant(full["wd"][:, i0:i1])
+            layer = dict(ln1=torch.ones(64, dtype=torch.bfloat16), ln2=torch.ones(64, dtype=torch.bfloat16), wqkv=wqkv,
+                         sqkv=sqkv, bqkv=torch.cat([full["bq"][qr], full["bk"][kr], full["bv"][kr]]), wo=wo, so=so,
+                         wgu=wgu, sgu=sgu, wd=wd, sd=sd)
+            out.append(dict(hq=len(qh), hkv=len(kh), embed=embed, norm_f=torch.ones(64, dtype=torch.bfloat16),
+                            lm_head=lm_head[r * V // tp:(r + 1) * V // tp], layers=[layer]))
+        return out
+
+    toks = torch.randint(0, V, (2, 5), generator=g)
+    l1 = Qwen2Oracle(Cfg, shards(1), 2, 8).forward(toks).float()
+    l2 = Qwen2Oracle(Cfg, shards(2), 2, 8).forward(toks).float()
+    assert l1.shape == l2.shape == (2, V)
+    assert float((l1 - l2).norm() / l1.norm()) < 0.05
