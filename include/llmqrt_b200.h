@@ -46,6 +46,8 @@ enum { /* element types */
 const char* llmqrt_last_error(void);
 /* ABI version; bumped when a signature changes. */
 int llmqrt_abi_version(void);
+/* Number of kernels this library has launched in the process so far (all threads). */
+long long llmqrt_launch_count(void);
 
 /* ------------------------------------------------------------------------------------------
  * Workspace.  Kernels that split the reduction dimension across thread blocks keep partial

@@ -33,6 +33,7 @@ P, I64, I32, F, SZ = c_void_p, c_int64, c_int, c_float, c_size_t
 _PROTOS = {
     "llmqrt_last_error": (c_char_p, []),
     "llmqrt_abi_version": (c_int, []),
+    "llmqrt_launch_count": (ctypes.c_longlong, []),
     "llmqrt_workspace_bytes": (SZ, []),
     "llmqrt_set_gemm_path": (c_int, [I32]),
     "llmqrt_quantize_int8": (c_int, [P, I32, I64, I64, I64, I32, P, P, P, F, P, P]),
@@ -143,6 +144,11 @@ def kernel_status(device: torch.device) -> int:
     """Reads (synchronously) the bounded-wait status word of the current stream's workspace."""
     ws = workspace(device)
     return int(ws[STATUS_OFFSET:STATUS_OFFSET + 4].view(torch.int32).item())
+
+
+def launch_count() -> int:
+    """Kernels launched by the library so far in this process."""
+    return int(_lib.llmqrt_launch_count())
 
 
 def set_gemm_path(path: int) -> None:

@@ -1,6 +1,7 @@
 // Process-wide pieces of the C ABI: error buffer, version, workspace size, device properties.
 #include "common.cuh"
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -33,6 +34,17 @@ int sm_count() {
   return cached;
 }
 
+static std::atomic<long long> g_launches{0};
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(LLMQRT_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return LLMQRT_OK;
+}
+
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
 int ensure_dynamic_smem(const void* func, int bytes) {
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, int> configured;
@@ -55,6 +67,8 @@ extern "C" {
 const char* llmqrt_last_error(void) { return llmqrt::last_error_buffer(); }
 
 int llmqrt_abi_version(void) { return 1; }
+
+long long llmqrt_launch_count(void) { return llmqrt::launch_count(); }
 
 // 64 KiB of arrival counters followed by 160 MiB of partial sums.  Every kernel that splits its
 // reduction clamps the number of slices so that its partials fit (8 slices of a 64 x 18944 fp32

@@ -34,11 +34,8 @@ int set_error(int code, const char* fmt, ...);  // formats into the buffer and r
       return ::llmqrt::set_error(LLMQRT_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
   } while (0)
 
-inline int check_launch(const char* what) {
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error(LLMQRT_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
-  return LLMQRT_OK;
-}
+// Called right after every kernel launch: reports a launch error and counts the launch (capi.cu).
+int check_launch(const char* what);
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

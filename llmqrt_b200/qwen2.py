@@ -201,6 +201,25 @@ class Qwen2Decoder:
         self.seqlens.fill_(S + 1)          # rows [0, pos] are valid once the step's K/V are written
         return torch.cat(out)
 
+    @torch.no_grad()
+    def decode_step_host(self, tokens_in: torch.Tensor, tokens_out: torch.Tensor) -> None:
+        """Serving-style step with HOST buffers: `tokens_in` / `tokens_out` are pinned CPU int64 [B] tensors.
+        Copies the ids to the device, runs one decode step, copies the sampled ids back and waits for them."""
+        dev_in = self._host_in if getattr(self, "_host_in", None) is not None else None
+        if dev_in is None:
+            dev_in = self._host_in = torch.empty(self.batch, dtype=torch.int64, device=self.device)
+        dev_in.copy_(tokens_in, non_blocking=True)
+        nxt = self.decode_step(dev_in, use_graph=True)
+        tokens_out.copy_(nxt, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def reset_position(self, pos: int) -> None:
+        """Rewind (or advance) the decode position; cache rows at and beyond `pos` will be overwritten."""
+        assert 0 <= pos < self.max_seq_len
+        self.pos = pos
+        self.pos_dev.fill_(pos)
+        self.seqlens.fill_(pos + 1)
+
     def _decode_body(self, tokens: torch.Tensor) -> torch.Tensor:
         h = self.embed[tokens]
         h, pending = self._layers_forward(h, self.batch, 1, decode=True)
