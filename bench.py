@@ -131,37 +131,45 @@ def gemm_roofline_pass(model, batch, torch):
         acts[K] = (torch.randint(-127, 128, (batch, K), generator=g, device=dev, dtype=torch.int8),
                    torch.rand(batch, generator=g, device=dev) * 1e-2)
 
-    def body():
-        for L_ in model.layers:
-            for w, s, b in ((L_.wqkv, L_.sqkv, L_.bqkv), (L_.wo, L_.so, None), (L_.wgu, L_.sgu, None),
-                            (L_.wd, L_.sd, None)):
-                xq, xs = acts[w.shape[1]]
-                ops.int8_linear_per_channel(xq, w, b, xs, s, dt)
+    names = {"qkv": ("wqkv", "sqkv", "bqkv"), "o": ("wo", "so", None), "gate_up": ("wgu", "sgu", None),
+             "down": ("wd", "sd", None)}
 
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(torch.cuda.current_stream(dev))
-    with torch.cuda.stream(side):
+    def timed(which):
+        def body():
+            for L_ in model.layers:
+                for nm in which:
+                    wn, sn, bn = names[nm]
+                    w = getattr(L_, wn)
+                    xq, xs = acts[w.shape[1]]
+                    ops.int8_linear_per_channel(xq, w, getattr(L_, bn) if bn else None, xs, getattr(L_, sn), dt)
         body()
-    torch.cuda.current_stream(dev).wait_stream(side)
-    torch.cuda.synchronize(dev)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        body()
-    graph.replay()
-    torch.cuda.synchronize(dev)
-    reps = 5
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            body()
         graph.replay()
-    e1.record()
-    torch.cuda.synchronize(dev)
-    secs = e0.elapsed_time(e1) / 1e3 / reps
+        torch.cuda.synchronize(dev)
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / 1e3 / reps
+
     L0 = model.layers[0]
-    shapes = [(L0.wqkv.shape, True), (L0.wo.shape, False), (L0.wgu.shape, False), (L0.wd.shape, False)]
-    nbytes = sum(gemm_bytes(batch, N, K, b) for (N, K), b in shapes) * len(model.layers)
-    launches = 4 * len(model.layers)
-    return nbytes / launches, secs / launches, launches
+    nlay = len(model.layers)
+    per_shape = {}
+    for nm, (wn, _, bn) in names.items():
+        N, K = getattr(L0, wn).shape
+        secs = timed([nm]) / nlay
+        b = gemm_bytes(batch, N, K, bn is not None)
+        per_shape[nm] = {"N": N, "K": K, "us": secs * 1e6, "gbs": b / secs / 1e9}
+    secs_all = timed(list(names))                       # the four GEMMs of every layer, in model order
+    nbytes = sum(gemm_bytes(batch, *getattr(L0, wn).shape, bn is not None) for wn, _, bn in names.values()) * nlay
+    launches = 4 * nlay
+    return nbytes / launches, secs_all / launches, per_shape
 
 
 def attn_roofline_pass(model, batch, ctx, torch):
@@ -312,7 +320,7 @@ def run_ours(args):
     secs_e2e = float(elapsed.item())
 
     # ---- dominant kernel --------------------------------------------------------------------------
-    bytes_per_launch, secs_per_launch, _ = gemm_roofline_pass(model, B, torch)
+    bytes_per_launch, secs_per_launch, gemm_shapes = gemm_roofline_pass(model, B, torch)
     attn_bytes, attn_secs = attn_roofline_pass(model, B, args.prompt_len + W + K // 2, torch)
     peak, peak_kind = measured_peak_hbm()
     achieved = bytes_per_launch / secs_per_launch / 1e9
@@ -335,7 +343,7 @@ def run_ours(args):
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None,
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": secs_per_launch * 1e6},
-            "extras": {"launches_per_step": launches_per_step,
+            "extras": {"launches_per_step": launches_per_step, "int8_gemm_by_shape": gemm_shapes,
                        "step_hbm_gbs": step_bytes / (secs / K) / 1e9, "step_hbm_frac": step_bytes / (secs / K) / 1e9 / peak,
                        "attn_decode_gbs": attn_bytes / attn_secs / 1e9, "attn_decode_frac": attn_bytes / attn_secs / 1e9 / peak,
                        "attn_decode_us": attn_secs * 1e6},

@@ -56,7 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources:
         obj = os.path.join(OBJDIR, os.path.basename(src)[:-3] + ".o")
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("LLMQRT_NVCC_FLAGS", "").split(), "-c", src, "-o", obj]
             if verbose:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append((src, cmd))

@@ -7,18 +7,30 @@
 // P is the operand whose rows become the 128 TMEM lanes, Q the one whose rows become TMEM columns.
 // For prefill-sized M the tokens are P and the weights Q.  For decode-sized M the roles are swapped
 // (weights are P, the few tokens are Q with BN = 32/64/128), so the tile is never mostly padding and
-// the kernel is a pure weight streamer; the reduction dimension is then split across thread blocks
-// to occupy every SM, with partial sums in the workspace and a last-arriver fix-up.
+// the kernel is a pure weight streamer.
+//
+// Split-K for skinny problems: when there are fewer tiles than SMs, the reduction dimension of a tile
+// is divided among the 2, 4 or 8 CTAs of a thread-block CLUSTER.  Each CTA accumulates its K range in
+// tensor memory, then the cluster reduce-scatters through distributed shared memory: CTA r owns
+// BN/S accumulator columns, every CTA stores its slice of those columns straight into r's shared
+// memory, and after one cluster barrier r adds the S contributions in rank order (deterministic) and
+// runs the epilogue.  No global scratch, no atomics, no second kernel.
 //
 // Warp roles (192 threads): warp 0 lane 0 issues TMA; warp 1 owns tensor memory and its lane 0
 // issues the MMAs; warps 2-5 run the epilogue (TMEM lane quadrant = warp id % 4).  All waits on
 // mbarriers are bounded; a time-out raises a block-wide abort flag and a status word in the
-// workspace, every role drains and the block frees its tensor memory before returning.
+// workspace, every role drains, reaches the cluster barriers and the block frees its tensor memory
+// before returning.
 //
-// No thread-block clusters and no multicast: every CTA fetches its own tiles.
+// Epilogue: accumulators go TMEM -> registers, the scales / bias are applied there (the per-column
+// ones come from a small shared-memory vector loaded once per tile), the 16-bit results are staged in
+// shared memory and leave for global memory as 16-byte vectors that are contiguous across lanes.
+//
+// No multicast anywhere: every CTA fetches its own tiles with plain TMA loads.
 #include "gemm_w8a8.cuh"
 #include "tc_primitives.cuh"
 
+#include <map>
 #include <mutex>
 #include <type_traits>
 
@@ -28,31 +40,35 @@ namespace {
 constexpr int kThreads = 192;
 constexpr int kBM = 128;           // rows of P per tile (UMMA M)
 constexpr int kRowBytes = 128;     // bytes of K per stage row (one swizzle span)
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kSmemBudget = 226 * 1024;   // of the 227 KiB a block may use
+constexpr int kChunk = 32;         // accumulator columns handled per epilogue step
+constexpr int kEpiStageBytes = 18 * 1024;  // staging tile for one chunk (worst case 128 x 32 x 4 B + padding)
 
 struct TcParams {
   int rows_p, rows_q;              // extents of P and Q (M/N or N/M)
   int k_blocks;                    // ceil(K bytes / 128)
-  int tiles_p, tiles_q, splits, kb_per_split;
+  int tiles_p, tiles_q, splits;    // splits == cluster size along K (1, 2, 4 or 8)
   int swap;                        // 0: P = tokens (i -> m, j -> n); 1: P = weights (i -> n, j -> m)
   int M, N;
   uint32_t idesc;
-  void* partials;
-  int* counters;
   unsigned* status;                // set to 1 if a bounded wait ran out
   Epilogue epi;
 };
 
 template <int BN> constexpr int stage_bytes() { return (kBM + BN) * kRowBytes; }
 template <int BN> constexpr int num_stages() {
-  int s = (kSmemBudget - 1024) / stage_bytes<BN>();
+  int s = (kSmemBudget - 1024 - kEpiStageBytes) / stage_bytes<BN>();
   return s > 8 ? 8 : s;
 }
+template <int BN> constexpr int smem_bytes() { return num_stages<BN>() * stage_bytes<BN>() + kEpiStageBytes + 1024; }
 template <int BN> constexpr uint32_t tmem_cols() { return 2 * BN < 32 ? 32 : 2 * BN; }
 
 template <typename AccT> __device__ __forceinline__ AccT acc_from_bits(uint32_t b);
 template <> __device__ __forceinline__ int acc_from_bits<int>(uint32_t b) { return (int)b; }
 template <> __device__ __forceinline__ float acc_from_bits<float>(uint32_t b) { return __uint_as_float(b); }
+template <typename AccT> __device__ __forceinline__ uint32_t acc_to_bits(AccT v);
+template <> __device__ __forceinline__ uint32_t acc_to_bits<int>(int v) { return (uint32_t)v; }
+template <> __device__ __forceinline__ uint32_t acc_to_bits<float>(float v) { return __float_as_uint(v); }
 
 __device__ __forceinline__ uint32_t pack16(float a, float b, int dtype) {
   if (dtype == LLMQRT_F16) {
@@ -63,6 +79,173 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, int dtype) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// Bulk asynchronous copy of `bytes` from this CTA's shared memory to the same offsets' counterpart in
+// CTA `cta_rank` of the cluster; completion is counted (complete_tx) on that CTA's mbarrier.
+// dst_local / bar_local are addresses in THIS CTA's window; mapa translates them to the peer's.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_local, uint32_t src_local, uint32_t bytes,
+                                                 uint32_t bar_local, uint32_t cta_rank) {
+  uint32_t dst, bar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(dst_local), "r"(cta_rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local), "r"(cta_rank));
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "r"(src_local), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// ---- epilogue --------------------------------------------------------------------------------------
+// Arithmetic of one output element.  `var` is the scale that changes with the accumulator column
+// (Q side), `fix` the one that belongs to the thread's row (P side); `var_first` says which of the two
+// the operator multiplies first (row scale first for the fp8 row-wise op, channel scale first for the
+// int8 per-channel op).
+struct EpiConsts {
+  int mode;
+  bool var_first, has_bias;
+  float alpha, fix_scale, fix_bias;
+};
+
+__device__ __forceinline__ float epi_value(const EpiConsts& c, float acc, float var_scale, float var_bias, bool swap) {
+  const float bias = swap ? c.fix_bias : var_bias;
+  if (c.mode == EPI_TENSOR) return __fmaf_rn(c.alpha, acc, bias);        // bias already multiplied by beta
+  const float s1 = c.var_first ? var_scale : c.fix_scale, s2 = c.var_first ? c.fix_scale : var_scale;
+  const float v = __fmul_rn(__fmul_rn(acc, s1), s2);
+  return c.has_bias ? __fadd_rn(v, bias) : v;
+}
+
+// Per-tile set-up: the Q-side scale / bias vectors go to shared memory, the P-side ones to registers.
+__device__ __forceinline__ EpiConsts epi_setup(const TcParams& prm, float alpha, int i, int j_base, int ncols_q,
+                                               int t, float* q_scale, float* q_bias) {
+  const Epilogue& e = prm.epi;
+  const bool scaled = e.mode == EPI_ROW_COL || e.mode == EPI_COL_ROW;
+  const float bmul = e.mode == EPI_TENSOR ? e.beta : 1.f;
+  for (int c = t; c < ncols_q; c += 128) {
+    const int j = j_base + c;
+    float s = 1.f, b = 0.f;
+    if (j < prm.rows_q) {
+      if (scaled) s = prm.swap ? e.row_scale[j] : e.col_scale[j];
+      if (!prm.swap && e.bias && e.mode != EPI_RAW) b = __fmul_rn(bmul, load_as_f32(e.bias, j, e.bias_dtype));
+    }
+    q_scale[c] = s;
+    q_bias[c] = b;
+  }
+  EpiConsts c;
+  c.mode = e.mode;
+  c.alpha = alpha;
+  c.has_bias = e.bias != nullptr;
+  c.var_first = (e.mode == EPI_ROW_COL) == (prm.swap != 0);
+  c.fix_scale = 1.f;
+  c.fix_bias = 0.f;
+  if (i < prm.rows_p) {
+    if (scaled) c.fix_scale = prm.swap ? e.col_scale[i] : e.row_scale[i];
+    if (prm.swap && e.bias && e.mode != EPI_RAW) c.fix_bias = __fmul_rn(bmul, load_as_f32(e.bias, i, e.bias_dtype));
+  }
+  return c;
+}
+
+// Staging-tile geometry.  es = bytes per output element (2, or 4 for raw / fp32 output).
+//   normal: [128 rows][kChunk cols] with a 16-byte pad per row; swap: [kChunk rows (m)][128 cols (n)] + pad.
+__device__ __forceinline__ int stage_pitch(bool swap, int es) { return (swap ? kBM : kChunk) * es + 16; }
+
+// Phase 1, eight accumulator columns at a time (kept short: this code runs cold, see the header):
+// apply the epilogue to r[0..8) = row `et`, columns c .. c+7 of the current chunk (q_scale / q_bias
+// already point at column c) and park the results in the staging tile.
+template <typename AccT>
+__device__ __forceinline__ void epi_stage_group8(const TcParams& prm, const EpiConsts& ec, const uint32_t (&r)[8],
+                                                 const float* q_scale, const float* q_bias, int c, int et,
+                                                 uint8_t* stage) {
+  const Epilogue& e = prm.epi;
+  const bool raw = e.mode == EPI_RAW, swap = prm.swap != 0;
+  const int es = (raw || e.out_dtype == LLMQRT_F32) ? 4 : 2;
+  const int pitch = stage_pitch(swap, es);
+  uint32_t w[8];
+  if (raw) {
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) w[jj] = r[jj];
+  } else {
+    const float4 s0 = *reinterpret_cast<const float4*>(q_scale), s1 = *reinterpret_cast<const float4*>(q_scale + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(q_bias), b1 = *reinterpret_cast<const float4*>(q_bias + 4);
+    const float qs[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const float qb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj)
+      w[jj] = __float_as_uint(epi_value(ec, (float)acc_from_bits<AccT>(r[jj]), qs[jj], qb[jj], swap));
+  }
+  if (swap) {
+    // element jj goes to staged row c + jj, column et: scalar stores, contiguous across lanes
+    if (es == 4) {
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) *reinterpret_cast<uint32_t*>(stage + (c + jj) * pitch + et * 4) = w[jj];
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj)
+        *reinterpret_cast<uint16_t*>(stage + (c + jj) * pitch + et * 2) =
+            (uint16_t)pack16(__uint_as_float(w[jj]), 0.f, e.out_dtype);
+    }
+  } else if (es == 4) {
+    uint4* dst = reinterpret_cast<uint4*>(stage + et * pitch + c * 4);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    *reinterpret_cast<uint4*>(stage + et * pitch + c * 2) =
+        make_uint4(pack16(__uint_as_float(w[0]), __uint_as_float(w[1]), e.out_dtype),
+                   pack16(__uint_as_float(w[2]), __uint_as_float(w[3]), e.out_dtype),
+                   pack16(__uint_as_float(w[4]), __uint_as_float(w[5]), e.out_dtype),
+                   pack16(__uint_as_float(w[6]), __uint_as_float(w[7]), e.out_dtype));
+  }
+}
+
+// Phase 2: staged block D[i0 .. i0+128, j0 .. j0+ncols) -> global memory, 16 bytes per thread and step.
+__device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8_t* stage, int ncols, int i0, int j0,
+                                                int t) {
+  const Epilogue& e = prm.epi;
+  const int es = (e.mode == EPI_RAW || e.out_dtype == LLMQRT_F32) ? 4 : 2;
+  const int per = 16 / es;                             // elements per 16-byte vector
+  const int pitch = stage_pitch(prm.swap != 0, es);
+  uint8_t* out = reinterpret_cast<uint8_t*>(e.out);
+  const bool base_ok = (reinterpret_cast<uintptr_t>(e.out) & 15) == 0 && (e.ldo % per) == 0;
+  // staged rows x vectors per staged row; in swap mode a staged row is one m with 128 n
+  const int srows = prm.swap ? ncols : kBM;
+  const int vec_per_row = (prm.swap ? kBM : kChunk) / per;
+  const int row_limit = prm.M, col_limit = prm.N;
+#pragma unroll 1
+  for (int idx = t; idx < srows * vec_per_row; idx += 128) {
+    const int sr = idx / vec_per_row, sv = idx - sr * vec_per_row;
+    const int m = prm.swap ? j0 + sr : i0 + sr;
+    const int n = (prm.swap ? i0 : j0) + sv * per;
+    const int n_end = prm.swap ? col_limit : min(col_limit, j0 + ncols);
+    if (m >= row_limit || n >= n_end) continue;
+    const uint4 val = *reinterpret_cast<const uint4*>(stage + sr * pitch + sv * 16);
+    uint8_t* dst = out + ((int64_t)m * e.ldo + n) * es;
+    if (base_ok && n + per <= n_end && (n % per) == 0) {
+      *reinterpret_cast<uint4*>(dst) = val;
+    } else {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(&val);
+      for (int k = 0; k < per && n + k < n_end; ++k)
+        for (int b = 0; b < es; ++b) dst[k * es + b] = src[k * es + b];
+    }
+  }
+}
+
+// Optional stage timestamps of block 0 (build with -DLLMQRT_TC_TRACE): 64-bit global-timer readings
+// stored after the status word of the workspace.
+#ifdef LLMQRT_TC_TRACE
+#define TC_TRACE(slot)                                                                                  \
+  do {                                                                                                  \
+    if (blockIdx.x == 0 && prm.status)                                                                  \
+      reinterpret_cast<unsigned long long*>(prm.status + 7)[slot] = tc::global_timer_ns();             \
+  } while (0)
+#else
+#define TC_TRACE(slot) do {} while (0)
+#endif
+
 template <int KIND, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q, TcParams prm) {
@@ -70,22 +253,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   constexpr int kStages = num_stages<BN>();
   constexpr int kStageBytes = stage_bytes<BN>();
   constexpr uint32_t kTmemCols = tmem_cols<BN>();
+  constexpr int kBurst = kStages >= 8 ? 4 : (kStages >= 4 ? 2 : 1);
+  static_assert(BN > 128 || kStages * kStageBytes >= 2 * kBM * BN * 4, "ring too small for the reduce buffers");
+  static_assert(kStages >= 3, "pipeline too shallow");
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern and the descriptors assume.
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage = tiles + kStages * kStageBytes;      // epilogue staging tile
   __shared__ __align__(8) uint64_t bar_full[kStages];
   __shared__ __align__(8) uint64_t bar_empty[kStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_reduce;         // split mode: counts the bytes of the incoming slices
+  __shared__ __align__(16) float q_scale[BN];
+  __shared__ __align__(16) float q_bias[BN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int s_ticket;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort = &abort_flag;
+  const int S = prm.splits;
+  const int my_split = S > 1 ? (int)cluster_ctarank() : 0;
 
   if (threadIdx.x == 0) {
+    TC_TRACE(0);
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
       tc::mbar_init(tc::smem_u32(&bar_full[s]), 1);
@@ -95,6 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       tc::mbar_init(tc::smem_u32(&bar_acc_full[b]), 1);
       tc::mbar_init(tc::smem_u32(&bar_acc_empty[b]), 128);
     }
+    tc::mbar_init(tc::smem_u32(&bar_reduce), 1);
     tc::mbar_fence_init();
     tc::tma_prefetch_descriptor(&tm_p);
     tc::tma_prefetch_descriptor(&tm_q);
@@ -107,40 +300,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) TC_TRACE(1);
 
-  const int num_work = prm.tiles_p * prm.tiles_q * prm.splits;
+  // Work items: split mode -> exactly one tile per cluster (grid = tiles * S, non persistent);
+  // otherwise a persistent walk over the tiles.
+  const int num_tiles = prm.tiles_p * prm.tiles_q;
+  const int first_tile = S > 1 ? (int)(blockIdx.x / S) : (int)blockIdx.x;
+  const int tile_step = S > 1 ? num_tiles : (int)gridDim.x;      // split mode: one iteration
+  // K range of this CTA (balanced, never empty because k_blocks >= 2 * S)
+  const int kb_begin = (int)((int64_t)my_split * prm.k_blocks / S);
+  const int kb_count = (int)((int64_t)(my_split + 1) * prm.k_blocks / S) - kb_begin;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
-      int stage = 0;
+      int stage_i = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int issued = 0;                 // loads issued in total (for draining on abort)
-      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int split = w % prm.splits;
-        const int tile = w / prm.splits;
+      int issued = 0;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
-        const int kb0 = split * prm.kb_per_split;
-        const int kb1 = min(kb0 + prm.kb_per_split, prm.k_blocks);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!tc::mbar_wait(tc::smem_u32(&bar_empty[stage]), phase ^ 1u, abort)) { ok = false; break; }
-          const uint32_t full = tc::smem_u32(&bar_full[stage]);
-          uint8_t* sp = tiles + stage * kStageBytes;
-          tc::mbar_arrive_expect_tx(full, kStageBytes);
-          // x coordinate in ELEMENTS of the tensor map's type; the maps are built on bytes for the
-          // 8-bit kinds and on 16-bit elements for fp16/bf16.
-          const int x = kb * (KIND == tc::MMA_F16 ? kRowBytes / 2 : kRowBytes);
-          tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
-          tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
-          ++issued;
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        // Blocks start at different K offsets so that they do not all pull the same activation rows
+        // out of L2 at the same moment; the accumulation order per tile stays fixed.
+        const int rot = (tp * 5 + tq * 3) % kb_count;
+        // K blocks are issued in bursts of kBurst consecutive blocks: the same weight rows are then
+        // requested at consecutive 128-byte offsets within nanoseconds, which the DRAM controller can
+        // serve from open pages (a lone 128-byte piece per row and visit is the worst case for HBM).
+        for (int it0 = 0; it0 < kb_count && ok; it0 += kBurst) {
+          const int nb = min(kBurst, kb_count - it0);
+          int s_w = stage_i;
+          uint32_t ph_w = phase;
+          for (int g = 0; g < nb; ++g) {               // wait until all slots of the burst are free
+            if (!tc::mbar_wait(tc::smem_u32(&bar_empty[s_w]), ph_w ^ 1u, abort)) { ok = false; break; }
+            if (++s_w == kStages) { s_w = 0; ph_w ^= 1u; }
+          }
+          if (!ok) break;
+          for (int g = 0; g < nb; ++g) {
+            int kr = it0 + g + rot;
+            if (kr >= kb_count) kr -= kb_count;
+            const int kb = kb_begin + kr;
+            const uint32_t full = tc::smem_u32(&bar_full[stage_i]);
+            uint8_t* sp = tiles + stage_i * kStageBytes;
+            tc::mbar_arrive_expect_tx(full, kStageBytes);
+            // x coordinate in ELEMENTS of the tensor map's type; the maps are built on bytes for the
+            // 8-bit kinds and on 16-bit elements for fp16/bf16.
+            const int x = kb * (KIND == tc::MMA_F16 ? kRowBytes / 2 : kRowBytes);
+            tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
+            tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
+            ++issued;
+            if (++stage_i == kStages) { stage_i = 0; phase ^= 1u; }
+          }
         }
       }
       if (!ok) {
-        // Drain: every load that was issued completes on its full barrier; wait for the most recent
-        // `min(issued, kStages)` of them (bounded) so that no copy is in flight when the block exits.
-        int s = stage;
+        // Drain: every load that was issued completes on its full barrier; wait (bounded) for the most
+        // recent min(issued, kStages) of them so that no copy is in flight when the block exits.
+        int s = stage_i;
         uint32_t ph = phase;
         for (int i = 0; i < min(issued, kStages); ++i) {
           if (--s < 0) { s = kStages - 1; ph ^= 1u; }
@@ -153,35 +368,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------
     if (lane == 0) {
-      int stage = 0;
+      int stage_i = 0;
       uint32_t phase = 0;
       uint32_t acc_phase[2] = {0, 0};
       int buf = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int split = w % prm.splits;
-        const int kb0 = split * prm.kb_per_split;
-        const int kb1 = min(kb0 + prm.kb_per_split, prm.k_blocks);
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         if (!tc::mbar_wait(tc::smem_u32(&bar_acc_empty[buf]), acc_phase[buf] ^ 1u, abort)) { ok = false; break; }
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!tc::mbar_wait(tc::smem_u32(&bar_full[stage]), phase, abort)) { ok = false; break; }
+        for (int it = 0; it < kb_count; ++it) {
+          if (!tc::mbar_wait(tc::smem_u32(&bar_full[stage_i]), phase, abort)) { ok = false; break; }
+          if (it == 0) TC_TRACE(2);
           tc::fence_after_sync();
-          const uint32_t sp = tc::smem_u32(tiles + stage * kStageBytes);
+          const uint32_t sp = tc::smem_u32(tiles + stage_i * kStageBytes);
           const uint64_t dp = tc::smem_desc_k_major_sw128(sp);
           const uint64_t dq = tc::smem_desc_k_major_sw128(sp + kBM * kRowBytes);
 #pragma unroll
           for (int j = 0; j < kRowBytes / 32; ++j) {
             // 32 bytes of K per instruction (32 8-bit or 16 16-bit elements): +2 in the >>4 address field.
             tc::mma_ss<KIND>(d_tmem, dp + (uint64_t)(2 * j), dq + (uint64_t)(2 * j), prm.idesc,
-                             (kb > kb0 || j > 0) ? 1u : 0u);
+                             (it > 0 || j > 0) ? 1u : 0u);
           }
-          tc::mma_commit(tc::smem_u32(&bar_empty[stage]));      // frees the stage once the MMAs retire
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          tc::mma_commit(tc::smem_u32(&bar_empty[stage_i]));    // frees the stage once the MMAs retire
+          if (++stage_i == kStages) { stage_i = 0; phase ^= 1u; }
         }
         if (!ok) break;
         tc::mma_commit(tc::smem_u32(&bar_acc_full[buf]));        // accumulator complete
+        TC_TRACE(3);
         acc_phase[buf] ^= 1u;
         buf ^= 1;
       }
@@ -192,112 +406,136 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     const int et = quad * 32 + lane;                   // row of the tile handled by this thread
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
-    const Epilogue& epi = prm.epi;
-    const float alpha = epi.alpha_dev ? *epi.alpha_dev : epi.alpha;
-    AccT* part = reinterpret_cast<AccT*>(prm.partials);
+    const float alpha = prm.epi.alpha_dev ? *prm.epi.alpha_dev : prm.epi.alpha;
 
-    for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
-      const int split = w % prm.splits;
-      const int tile = w / prm.splits;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
       const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
+      EpiConsts ec;
+      if (S == 1) {
+        epi_barrier();                                 // previous tile no longer reads q_scale / q_bias
+        ec = epi_setup(prm, alpha, tp * kBM + et, tq * BN, BN, et, q_scale, q_bias);
+      }
       // The four epilogue warps must agree on leaving the loop: OR the failure over all 128 threads.
       const bool failed = !tc::mbar_wait(tc::smem_u32(&bar_acc_full[buf]), acc_phase[buf], abort);
       if (tc::named_barrier_or(2, 128, failed)) break;
       tc::fence_after_sync();
       acc_phase[buf] ^= 1u;
+      if (threadIdx.x == 64) TC_TRACE(4);
+      if (S > 1) break;                                // split mode: the reduce-scatter below takes over
 
-      const int i = tp * kBM + et;                     // global row of P
-      const bool row_ok = i < prm.rows_p;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
-
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tc::tmem_ld_32x32(taddr + (uint32_t)c0, r);
-        tc::tmem_ld_wait();
-        const int j0 = tq * BN + c0;                   // global row of Q for r[0]
-        if (j0 >= prm.rows_q) continue;                // warp-uniform
-        if (prm.splits > 1) {
-          // partial sums, layout [split][M][N]
-          AccT* mine = part + (int64_t)split * prm.M * prm.N;
-          if (row_ok) {
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const int j = j0 + jj;
-              if (j < prm.rows_q) {
-                const int64_t m = prm.swap ? j : i, n = prm.swap ? i : j;
-                mine[m * prm.N + n] = acc_from_bits<AccT>(r[jj]);
-              }
-            }
-          }
-        } else if (prm.swap) {
-          // lane -> n (contiguous in memory), jj -> m: coalesced 16-bit stores across the warp
-          if (row_ok) {
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const int j = j0 + jj;
-              if (j < prm.rows_q) epilogue_store<AccT>(epi, acc_from_bits<AccT>(r[jj]), j, i, alpha);
-            }
-          }
-        } else if (row_ok) {
-          // thread -> m, jj -> 32 consecutive n: vector stores when aligned
-          const bool vec = epi.mode != EPI_RAW && epi.out_dtype != LLMQRT_F32 && j0 + 32 <= prm.rows_q &&
-                           (epi.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0);
-          if (vec) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int jj = 0; jj < 32; jj += 2) {
-              const float v0 = epilogue_value(epi, (float)acc_from_bits<AccT>(r[jj]), i, j0 + jj, alpha);
-              const float v1 = epilogue_value(epi, (float)acc_from_bits<AccT>(r[jj + 1]), i, j0 + jj + 1, alpha);
-              packed[jj / 2] = pack16(v0, v1, epi.out_dtype);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(epi.out) + (int64_t)i * epi.ldo + j0);
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-              dst[q4] = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-          } else {
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const int j = j0 + jj;
-              if (j < prm.rows_q) epilogue_store<AccT>(epi, acc_from_bits<AccT>(r[jj]), i, j, alpha);
-            }
-          }
+      for (int c0 = 0; c0 < BN; c0 += kChunk) {
+        const int j0 = tq * BN + c0;                   // global row of Q of the first column of the chunk
+        if (j0 >= prm.rows_q) break;
+        epi_barrier();                                 // staging tile drained by everyone
+#pragma unroll 1
+        for (int c = 0; c < kChunk; c += 8) {
+          uint32_t r[8];
+          tc::tmem_ld_32x8(taddr + (uint32_t)(c0 + c), r);
+          tc::tmem_ld_wait();
+          epi_stage_group8<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
+        epi_barrier();
+        epi_drain_chunk(prm, stage, min(kChunk, prm.rows_q - j0), tp * kBM, j0, et);
       }
       // accumulator buffer may be overwritten by the next-but-one tile
       tc::fence_before_sync();
       tc::mbar_arrive(tc::smem_u32(&bar_acc_empty[buf]));
       buf ^= 1;
-
-      if (prm.splits > 1) {
-        // last arriver of this tile sums the slices in order and applies the epilogue
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) s_ticket = atomicAdd(&prm.counters[tile], 1);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const bool last = s_ticket == prm.splits - 1;
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // s_ticket may be rewritten after this point
-        if (last) {
-          __threadfence();
-          if (row_ok) {
-            for (int jj = 0; jj < BN; ++jj) {
-              const int j = tq * BN + jj;
-              if (j >= prm.rows_q) break;
-              const int64_t m = prm.swap ? j : i, n = prm.swap ? i : j;
-              AccT sum = 0;
-              for (int s = 0; s < prm.splits; ++s) sum += __ldcg(part + ((int64_t)s * prm.M + m) * prm.N + n);
-              epilogue_store<AccT>(epi, sum, m, n, alpha);
-            }
-          }
-          if (threadIdx.x == 64) prm.counters[tile] = 0;
-        }
-      }
     }
   }
 
+  // ------------------------------- cluster reduce-scatter (split mode) --------------------------
+  if constexpr (BN <= 128) {
+  if (S > 1) {
+    // The pipeline ring is dead once a CTA's MMAs have retired.  It is reused as
+    //   recv = ring[0, BN*512)          [source rank][owned column][128 rows] 32-bit words
+    //   send = ring[BN*512, BN*1024)    [accumulator column][128 rows]
+    // Each CTA parks its accumulator in `send`, and after a cluster barrier (every ring dead) one
+    // thread pushes slice o of `send` into `recv` of CTA o with a bulk shared->shared copy that
+    // completes on o's `bar_reduce`.
+    const int cpo = BN / S;                            // accumulator columns owned by each CTA
+    const uint32_t slice_bytes = (uint32_t)cpo * kBM * 4;
+    uint32_t* send = reinterpret_cast<uint32_t*>(tiles + BN * kBM * 4);
+    const bool healthy = abort_flag == 0;              // own MMAs finished (epilogue warps waited for them)
+    const int quad = warp & 3, et = quad * 32 + lane;
+    const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
+    EpiConsts ec;
+    if (warp >= 2 && healthy) {
+      const float alpha = prm.epi.alpha_dev ? *prm.epi.alpha_dev : prm.epi.alpha;
+      // q_scale / q_bias cover only the columns this CTA owns
+      ec = epi_setup(prm, alpha, tp * kBM + et, tq * BN + my_split * cpo, cpo, et, q_scale, q_bias);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 8) {
+        uint32_t r[8];
+        tc::tmem_ld_32x8(taddr + (uint32_t)c0, r);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) send[(c0 + jj) * kBM + et] = r[jj];
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> bulk-copy reads
+      if (threadIdx.x == 64) TC_TRACE(7);
+      if (threadIdx.x == 64) tc::mbar_arrive_expect_tx(tc::smem_u32(&bar_reduce), slice_bytes * (uint32_t)S);
+    }
+    // Cluster barrier: every ring is dead, every `send` is complete, every `bar_reduce` is armed.
+    __syncwarp();
+    cluster_sync_all();
+    if (threadIdx.x == 64 && healthy) {
+      for (int o = 0; o < S; ++o)
+        bulk_copy_to_cta(tc::smem_u32(tiles) + (uint32_t)my_split * slice_bytes,
+                         tc::smem_u32(send) + (uint32_t)o * slice_bytes, slice_bytes, tc::smem_u32(&bar_reduce),
+                         (uint32_t)o);
+    }
+    if (threadIdx.x == 64) TC_TRACE(8);
+    bool reduce_ok = false;
+    if (warp >= 2) {
+      const bool failed = !healthy || !tc::mbar_wait(tc::smem_u32(&bar_reduce), 0u, abort);
+      reduce_ok = !tc::named_barrier_or(2, 128, failed);
+    }
+    if (threadIdx.x == 64) TC_TRACE(9);
+    if (warp >= 2 && reduce_ok) {
+      const AccT* rbuf = reinterpret_cast<const AccT*>(tiles);
+#pragma unroll 1
+      for (int c0 = 0; c0 < cpo; c0 += kChunk) {
+        const int j0 = tq * BN + my_split * cpo + c0;
+        if (j0 >= prm.rows_q) break;
+        const int ncols = min(min(kChunk, cpo - c0), prm.rows_q - j0);
+        epi_barrier();
+#pragma unroll 1
+        for (int c = 0; c < min(kChunk, cpo - c0); c += 8) {
+          AccT sum[8];
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) sum[jj] = 0;
+#pragma unroll 1
+          for (int s = 0; s < S; ++s) {                // rank order: deterministic
+            const AccT* src = rbuf + (s * cpo + c0 + c) * kBM + et;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) sum[jj] += src[jj * kBM];
+          }
+          uint32_t r[8];
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) r[jj] = acc_to_bits<AccT>(sum[jj]);
+          epi_stage_group8<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
+        }
+        epi_barrier();
+        epi_drain_chunk(prm, stage, ncols, tp * kBM, j0, et);
+      }
+    }
+    // Nobody leaves while a peer may still be copying out of its `send` buffer: an owner passes this
+    // barrier only after all the slices addressed to it have landed.
+    if (threadIdx.x == 64) TC_TRACE(10);
+    __syncwarp();
+    cluster_sync_all();
+  }
+  }
+
   // ------------------------------- teardown ---------------------------------------
+  if (threadIdx.x == 64) TC_TRACE(5);
   tc::fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) TC_TRACE(6);
   if (warp == 1) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
@@ -341,22 +579,81 @@ int make_operand_map(CUtensorMap* map, const void* base, int elt_bytes, int64_t 
 }
 
 template <int KIND, int BN>
-int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const TcParams& prm, int grid, cudaStream_t st) {
-  constexpr int smem = num_stages<BN>() * stage_bytes<BN>() + 1024;
+cudaLaunchConfig_t make_config(int grid, int cluster, cudaStream_t st, cudaLaunchAttribute* attr) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes<BN>();
+  cfg.stream = st;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cfg;
+}
+
+// How many clusters of `cluster` CTAs of this kernel can be resident at once (cached per device).
+template <int KIND, int BN>
+int max_active_clusters(int cluster) {
+  static std::mutex mu;
+  static std::map<std::pair<int, int>, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find({dev, cluster});
+  if (it != cache.end()) return it->second;
   auto kern = gemm_tc_kernel<KIND, BN>;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
-  kern<<<grid, kThreads, smem, st>>>(tm_p, tm_q, prm);
+  int n = 0;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>()) == LLMQRT_OK) {
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = make_config<KIND, BN>(cluster, cluster, nullptr, attr);
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+  }
+  cache[{dev, cluster}] = n;
+  return n;
+}
+
+template <int KIND, int BN>
+int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaStream_t st) {
+  auto kern = gemm_tc_kernel<KIND, BN>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>())) return rc;
+  const int sms = sm_count();
+  const int tiles = prm.tiles_p * prm.tiles_q;
+  int splits = 1;
+  if (BN <= 128 && tiles < sms) {
+    // Pick the cluster size (1, 2, 4, 8) with the smallest estimated time: waves of co-resident
+    // clusters x (K blocks per CTA + a fixed per-CTA cost of about eight K blocks for pipeline fill,
+    // reduce-scatter and epilogue).
+    const float fixed = 8.f;
+    float best = (float)ceil_div(tiles, sms) * ((float)prm.k_blocks + fixed);
+    for (int s = 2; s <= 8; s *= 2) {
+      if (prm.k_blocks < 2 * s || BN % s != 0 || BN / s < 8) continue;
+      const int active = max_active_clusters<KIND, BN>(s);
+      if (active <= 0) continue;
+      const float t = (float)ceil_div(tiles, active) * ((float)prm.k_blocks / s + fixed);
+      if (t < best) { best = t; splits = s; }
+    }
+  }
+  prm.splits = splits;
+  const int grid = splits > 1 ? tiles * splits : (tiles < sms ? tiles : sms);
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t cfg = make_config<KIND, BN>(grid, splits, st, attr);
+  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_p, tm_q, prm));
   return check_launch("gemm_tc");
 }
 
 template <int KIND>
-int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const TcParams& prm, int grid,
-              cudaStream_t st) {
+int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const TcParams& prm, cudaStream_t st) {
   switch (bn) {
-    case 32: return launch<KIND, 32>(tm_p, tm_q, prm, grid, st);
-    case 64: return launch<KIND, 64>(tm_p, tm_q, prm, grid, st);
-    case 128: return launch<KIND, 128>(tm_p, tm_q, prm, grid, st);
-    default: return launch<KIND, 256>(tm_p, tm_q, prm, grid, st);
+    case 32: return launch<KIND, 32>(tm_p, tm_q, prm, st);
+    case 64: return launch<KIND, 64>(tm_p, tm_q, prm, st);
+    case 128: return launch<KIND, 128>(tm_p, tm_q, prm, st);
+    default: return launch<KIND, 256>(tm_p, tm_q, prm, st);
   }
 }
 
@@ -383,21 +680,6 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   prm.k_blocks = (int)ceil_div(K * elt, kRowBytes);
   prm.tiles_p = (int)ceil_div(prm.rows_p, kBM);
   prm.tiles_q = (int)ceil_div(prm.rows_q, bn);
-
-  const int sms = sm_count();
-  const int tiles = prm.tiles_p * prm.tiles_q;
-  int splits = 1;
-  if (tiles < sms && workspace) {
-    splits = sms / tiles;
-    const int max_by_k = prm.k_blocks / 4 > 0 ? prm.k_blocks / 4 : 1;      // at least 4 K blocks per slice
-    if (splits > max_by_k) splits = max_by_k;
-    while (splits > 1 && (size_t)splits * M * N * 4 > LLMQRT_WS_PARTIAL_BYTES) --splits;
-    if (tiles > LLMQRT_WS_NUM_COUNTERS) splits = 1;
-  }
-  prm.kb_per_split = (int)ceil_div(prm.k_blocks, splits);
-  prm.splits = (int)ceil_div(prm.k_blocks, prm.kb_per_split);               // no empty slice
-  prm.partials = workspace ? ws_partials(workspace) : nullptr;
-  prm.counters = workspace ? ws_counters(workspace) : nullptr;
   prm.status = workspace ? ws_scalars(workspace) + 1 : nullptr;
 
   // A/B formats of the instruction follow P/Q.
@@ -415,11 +697,9 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   if (int rc = make_operand_map(&tm_p, p_base, elt, prm.rows_p, K, prm.swap ? ldw : lda, kBM)) return rc;
   if (int rc = make_operand_map(&tm_q, q_base, elt, prm.rows_q, K, prm.swap ? lda : ldw, bn)) return rc;
 
-  const int work = tiles * prm.splits;
-  const int grid = work < sms ? work : sms;
-  if (mk == tc::MMA_I8) return launch_bn<tc::MMA_I8>(bn, tm_p, tm_q, prm, grid, st);
-  if (mk == tc::MMA_F8) return launch_bn<tc::MMA_F8>(bn, tm_p, tm_q, prm, grid, st);
-  return launch_bn<tc::MMA_F16>(bn, tm_p, tm_q, prm, grid, st);
+  if (mk == tc::MMA_I8) return launch_bn<tc::MMA_I8>(bn, tm_p, tm_q, prm, st);
+  if (mk == tc::MMA_F8) return launch_bn<tc::MMA_F8>(bn, tm_p, tm_q, prm, st);
+  return launch_bn<tc::MMA_F16>(bn, tm_p, tm_q, prm, st);
 }
 
 }  // namespace llmqrt

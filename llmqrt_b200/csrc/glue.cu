@@ -1,104 +1,219 @@
 // Block glue of the decode step: RMSNorm (+ residual add, + int8 quantization), rotary embedding
 // fused with the KV-cache write, SiLU(gate) * up (+ int8 quantization).  Each kernel replaces a
 // chain of small torch ops and keeps their rounding points (fp32 math, one rounding to the 16-bit
-// activation type after every op of the chain).  All are HBM/L2-bound row kernels: one block per
-// token row, 128-bit accesses, the row staged once in shared memory.
+// activation type after every op of the chain).
+//
+// The row kernels (RMSNorm, SiLU*up) are HBM/L2-bound.  A token row is handled by a thread-block
+// cluster of 1, 2, 4 or 8 CTAs, each owning a contiguous slice of the row; the row-wide reductions
+// (sum of squares, absmax) are exchanged through distributed shared memory.  With the 64 rows of a
+// decode step this spreads the work over every SM instead of 64 of them.  128-bit accesses whenever
+// the slice is 16-byte aligned; the computed slice stays in shared memory for the quantization pass.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace llmqrt {
 namespace {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ float block_reduce(float v, bool is_max) {
+template <bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v) {
   __shared__ float red[kThreads / 32];
   __shared__ float result;
-  v = is_max ? warp_max(v) : warp_sum(v);
-  __syncthreads();                                  // protects `red`/`result` between successive calls
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  __syncthreads();                                  // protects `red` / `result` between successive calls
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float w = threadIdx.x < kThreads / 32 ? red[threadIdx.x] : (is_max ? 0.f : 0.f);
-    w = is_max ? warp_max(w) : warp_sum(w);
+    float w = threadIdx.x < kThreads / 32 ? red[threadIdx.x] : 0.f;
+    w = IS_MAX ? warp_max(w) : warp_sum(w);
     if (threadIdx.x == 0) result = w;
   }
   __syncthreads();
   return result;
 }
 
-// Per-token int8 quantization of a row already rounded to T and held in shared memory; same
-// arithmetic as the stand-alone quantizer (scale = T(T(max(absmax,1e-5)) * (1/127)), q = rint(T(x/scale))).
-template <typename T>
-__device__ __forceinline__ void quantize_row_int8(const T* __restrict__ row_s, int64_t n, float amax,
-                                                  int8_t* __restrict__ q, float* __restrict__ scale_out) {
-  float s = round_to<T>(fmaxf(amax, 1e-5f));
-  s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
-  if (threadIdx.x == 0) *scale_out = s;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = rintf(round_to<T>(__fdiv_rn(to_f32<T>(row_s[i]), s)));
-    v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
-    q[i] = (int8_t)(int)v;
+// Combines the per-CTA values of a cluster in rank order (same result in every CTA).  `slot` is a
+// shared-memory word of this CTA that the other CTAs of the cluster read remotely.
+template <bool IS_MAX>
+__device__ __forceinline__ float cluster_reduce(float block_val, float* slot, int cluster_size) {
+  if (cluster_size == 1) return block_val;
+  cg::cluster_group cluster = cg::this_cluster();
+  if (threadIdx.x == 0) *slot = block_val;
+  cluster.sync();
+  float r = 0.f;
+  for (int c = 0; c < cluster_size; ++c) {
+    const float v = *cluster.map_shared_rank(slot, c);
+    r = IS_MAX ? fmaxf(r, v) : r + v;
+  }
+  return r;
+}
+
+template <typename T, int U> struct Pack { T v[U]; };
+
+template <typename T, bool VEC>
+__device__ __forceinline__ void load_unit(const T* p, int64_t unit, T (&out)[VEC ? 8 : 1]) {
+  if constexpr (VEC) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p + unit * 8);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = e[j];
+  } else {
+    out[0] = p[unit];
+  }
+}
+template <typename T, bool VEC>
+__device__ __forceinline__ void store_unit(T* p, int64_t unit, const T (&in)[VEC ? 8 : 1]) {
+  if constexpr (VEC) {
+    *reinterpret_cast<uint4*>(p + unit * 8) = *reinterpret_cast<const uint4*>(in);
+  } else {
+    p[unit] = in[0];
   }
 }
 
-template <typename T>
+// Per-token int8 quantization of a row slice already rounded to T and held in shared memory; same
+// arithmetic as the stand-alone quantizer (scale = T(T(max(absmax,1e-5)) * (1/127)), q = rint(T(x/scale))).
+template <typename T, bool VEC>
+__device__ __forceinline__ void quantize_slice_int8(const T* __restrict__ row_s, int64_t units, float amax,
+                                                    int8_t* __restrict__ q, float* __restrict__ scale_out) {
+  constexpr int U = VEC ? 8 : 1;
+  float s = round_to<T>(fmaxf(amax, 1e-5f));
+  s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
+  if (scale_out && threadIdx.x == 0) *scale_out = s;
+  for (int64_t u = threadIdx.x; u < units; u += blockDim.x) {
+    T e[U];
+    load_unit<T, VEC>(row_s, u, e);
+    __align__(8) int8_t o[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      float v = rintf(round_to<T>(__fdiv_rn(to_f32<T>(e[j]), s)));
+      v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
+      o[j] = (int8_t)(int)v;
+    }
+    if constexpr (VEC) *reinterpret_cast<uint2*>(q + u * 8) = *reinterpret_cast<const uint2*>(o);
+    else q[u] = o[0];
+  }
+}
+
+// grid = (cluster_size, M): blockIdx.x = rank in the row's cluster, blockIdx.y = row.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ x_out,
                const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
-               float* __restrict__ scale_f32, int64_t H) {
+               float* __restrict__ scale_f32, int64_t H, int64_t slice) {
+  constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float slot_ss, slot_amax;
   T* row = reinterpret_cast<T*>(smem);
-  const int64_t m = blockIdx.x;
-  const T* xr = x + m * H;
+  const int cl = gridDim.x, rank = blockIdx.x;
+  const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
+  const int64_t len = max((int64_t)0, min(slice, H - c0)), units = len / U;
+  const int64_t off = m * H + c0;
   float ss = 0.f;
-  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = to_f32<T>(xr[i]);
-    if (residual) v = round_to<T>(v + to_f32<T>(residual[m * H + i]));    // h = x + r in T
-    T hv = from_f32<T>(v);
-    if (x_out) x_out[m * H + i] = hv;
-    row[i] = hv;
-    ss += v * v;
+  for (int64_t u = threadIdx.x; u < units; u += blockDim.x) {
+    T e[U], r[U];
+    load_unit<T, VEC>(x + off, u, e);
+    if (residual) load_unit<T, VEC>(residual + off, u, r);
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      float v = to_f32<T>(e[j]);
+      if (residual) v = round_to<T>(v + to_f32<T>(r[j]));                 // h = x + r in T
+      e[j] = from_f32<T>(v);
+      ss += v * v;
+    }
+    if (x_out) store_unit<T, VEC>(x_out + off, u, e);
+    store_unit<T, VEC>(row, u, e);
   }
-  ss = block_reduce(ss, false);
+  ss = cluster_reduce<false>(block_reduce<false>(ss), &slot_ss, cl);
   const float inv = rsqrtf(ss / (float)H + eps);
   float amax = 0.f;
-  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
-    const float n = round_to<T>(to_f32<T>(row[i]) * inv);                 // (x32 * inv).to(T)
-    const float o = round_to<T>(to_f32<T>(weight[i]) * n);                // weight * that, in T
-    const T ov = from_f32<T>(o);
-    if (y) y[m * H + i] = ov;
-    row[i] = ov;
-    amax = fmaxf(amax, fabsf(o));
+  for (int64_t u = threadIdx.x; u < units; u += blockDim.x) {
+    T e[U], w[U];
+    load_unit<T, VEC>(row, u, e);
+    load_unit<T, VEC>(weight + c0, u, w);
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const float n = round_to<T>(to_f32<T>(e[j]) * inv);                 // (x32 * inv).to(T)
+      const float o = round_to<T>(to_f32<T>(w[j]) * n);                   // weight * that, in T
+      e[j] = from_f32<T>(o);
+      amax = fmaxf(amax, fabsf(o));
+    }
+    if (y) store_unit<T, VEC>(y + off, u, e);
+    store_unit<T, VEC>(row, u, e);
   }
   if (q) {
-    amax = block_reduce(amax, true);
-    quantize_row_int8<T>(row, H, amax, q + m * H, scale_f32 + m);
+    amax = cluster_reduce<true>(block_reduce<true>(amax), &slot_amax, cl);
+    __syncthreads();
+    quantize_slice_int8<T, VEC>(row, units, amax, q + off, rank == 0 ? scale_f32 + m : nullptr);
   }
+  if (cl > 1) cg::this_cluster().sync();             // nobody leaves while its slots may still be read
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 silu_mul_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, int8_t* __restrict__ q,
-                float* __restrict__ scale_f32, int64_t I) {
+                float* __restrict__ scale_f32, int64_t I, int64_t slice) {
+  constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float slot_amax;
   T* row = reinterpret_cast<T*>(smem);
-  const int64_t m = blockIdx.x;
-  const T* gr = gate_up + m * ld;
+  const int cl = gridDim.x, rank = blockIdx.x;
+  const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
+  const int64_t len = max((int64_t)0, min(slice, I - c0)), units = len / U;
+  const T* gr = gate_up + m * ld + c0;
   const T* ur = gr + I;
   float amax = 0.f;
-  for (int64_t i = threadIdx.x; i < I; i += blockDim.x) {
-    const float g = to_f32<T>(gr[i]);
-    const float act = round_to<T>(g / (1.0f + expf(-g)));                 // silu in T
-    const float h = round_to<T>(act * to_f32<T>(ur[i]));                  // * up, in T
-    const T hv = from_f32<T>(h);
-    if (y) y[m * I + i] = hv;
-    if (q) row[i] = hv;
-    amax = fmaxf(amax, fabsf(h));
+  for (int64_t u = threadIdx.x; u < units; u += blockDim.x) {
+    T g[U], up[U];
+    load_unit<T, VEC>(gr, u, g);
+    load_unit<T, VEC>(ur, u, up);
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const float gv = to_f32<T>(g[j]);
+      const float act = round_to<T>(gv / (1.0f + expf(-gv)));             // silu in T
+      const float h = round_to<T>(act * to_f32<T>(up[j]));                // * up, in T
+      g[j] = from_f32<T>(h);
+      amax = fmaxf(amax, fabsf(h));
+    }
+    if (y) store_unit<T, VEC>(y + m * I + c0, u, g);
+    if (q) store_unit<T, VEC>(row, u, g);
   }
   if (q) {
-    amax = block_reduce(amax, true);
-    quantize_row_int8<T>(row, I, amax, q + m * I, scale_f32 + m);
+    amax = cluster_reduce<true>(block_reduce<true>(amax), &slot_amax, cl);
+    __syncthreads();
+    quantize_slice_int8<T, VEC>(row, units, amax, q + m * I + c0, rank == 0 ? scale_f32 + m : nullptr);
   }
+  if (cl > 1) cg::this_cluster().sync();
+}
+
+// Cluster size for a row kernel: as many CTAs per row as needed to put about two CTAs on every SM,
+// limited to 8 and to slices that stay 16-byte aligned.
+int pick_cluster(int64_t M, int64_t row_len) {
+  int cl = 1;
+  while (cl < 8 && M * cl < 2 * sm_count() && row_len % (cl * 2 * 8) == 0 && row_len / (cl * 2) >= 256) cl *= 2;
+  return cl;
+}
+
+template <typename Kern, typename... Args>
+int launch_row_kernel(Kern kern, int cl, int64_t M, size_t smem, cudaStream_t st, Args... args) {
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)cl, (unsigned)M, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, args...));
+  return LLMQRT_OK;
 }
 
 // One block per (token, head); thread i rotates the pair (i, i + d/2).
@@ -137,6 +252,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ q, int64_t q_token_stride, 
   }
 }
 
+inline bool aligned16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 }  // namespace
 }  // namespace llmqrt
 
@@ -147,46 +264,63 @@ extern "C" {
 int llmqrt_rmsnorm(const void* x, const void* residual, void* x_out, const void* weight, float eps, void* y,
                    int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H, llmqrt_stream_t stream) {
   LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "rmsnorm: dtype must be fp16 or bf16");
-  LLMQRT_REQUIRE(M >= 0 && H > 0 && M < (1ll << 31) && H * 2 <= 200 * 1024, "rmsnorm: bad shape");
+  LLMQRT_REQUIRE(M >= 0 && H > 0 && M < 65536ll * 32768 && H * 2 <= 200 * 1024, "rmsnorm: bad shape");
   if (M == 0) return LLMQRT_OK;
   LLMQRT_REQUIRE(x && weight && (y || q), "rmsnorm: null pointer");
   LLMQRT_REQUIRE(!q || scale_f32, "rmsnorm: quantized output needs scale_f32");
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)H * 2;
-#define LLMQRT_RUN(T)                                                                                              \
-  do {                                                                                                             \
-    auto kern = rmsnorm_kernel<T>;                                                                                 \
-    if (smem > 48 * 1024)                                                                                          \
-      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;          \
-    kern<<<(unsigned)M, kThreads, smem, st>>>(reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(residual), \
-                                              reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), eps,  \
-                                              reinterpret_cast<T*>(y), q, scale_f32, H);                            \
-  } while (0)
-  if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
+  const bool vec = H % 8 == 0 && aligned16(x) && aligned16(residual) && aligned16(x_out) && aligned16(weight) &&
+                   aligned16(y) && (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+  // gridDim.y carries the row: rows beyond 65535 are launched in panels
+  const int cl = vec ? pick_cluster(M, H) : 1;
+  const int64_t slice = H / cl;
+  const size_t smem = (size_t)slice * 2;
+  for (int64_t m0 = 0; m0 < M; m0 += 65535) {
+    const int64_t mc = (M - m0 < 65535) ? (M - m0) : 65535;
+    const int64_t o = m0 * H;
+    int rc;
+#define LLMQRT_RUN(T, V)                                                                                          \
+  rc = launch_row_kernel(rmsnorm_kernel<T, V>, cl, mc, smem, st, reinterpret_cast<const T*>(x) + o,                \
+                         residual ? reinterpret_cast<const T*>(residual) + o : (const T*)nullptr,                  \
+                         x_out ? reinterpret_cast<T*>(x_out) + o : (T*)nullptr, reinterpret_cast<const T*>(weight), \
+                         eps, y ? reinterpret_cast<T*>(y) + o : (T*)nullptr, q ? q + o : (int8_t*)nullptr,          \
+                         scale_f32 ? scale_f32 + m0 : (float*)nullptr, H, slice)
+    if (dtype == LLMQRT_F16) { if (vec) LLMQRT_RUN(__half, true); else LLMQRT_RUN(__half, false); }
+    else { if (vec) LLMQRT_RUN(__nv_bfloat16, true); else LLMQRT_RUN(__nv_bfloat16, false); }
 #undef LLMQRT_RUN
-  return check_launch("rmsnorm");
+    if (rc) return rc;
+    if (int rc2 = check_launch("rmsnorm")) return rc2;
+  }
+  return LLMQRT_OK;
 }
 
 int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M,
                     int64_t I, llmqrt_stream_t stream) {
   LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "silu_mul: dtype must be fp16 or bf16");
-  LLMQRT_REQUIRE(M >= 0 && I > 0 && ld >= 2 * I && M < (1ll << 31) && I * 2 <= 200 * 1024, "silu_mul: bad shape");
+  LLMQRT_REQUIRE(M >= 0 && I > 0 && ld >= 2 * I && M < 65536ll * 32768 && I * 2 <= 200 * 1024, "silu_mul: bad shape");
   if (M == 0) return LLMQRT_OK;
   LLMQRT_REQUIRE(gate_up && (y || q), "silu_mul: null pointer");
   LLMQRT_REQUIRE(!q || scale_f32, "silu_mul: quantized output needs scale_f32");
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = q ? (size_t)I * 2 : 0;
-#define LLMQRT_RUN(T)                                                                                        \
-  do {                                                                                                       \
-    auto kern = silu_mul_kernel<T>;                                                                          \
-    if (smem > 48 * 1024)                                                                                    \
-      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;    \
-    kern<<<(unsigned)M, kThreads, smem, st>>>(reinterpret_cast<const T*>(gate_up), ld, reinterpret_cast<T*>(y), q, \
-                                              scale_f32, I);                                                  \
-  } while (0)
-  if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
+  const bool vec = I % 8 == 0 && ld % 8 == 0 && aligned16(gate_up) && aligned16(y) &&
+                   (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+  const int cl = vec ? pick_cluster(M, I) : 1;
+  const int64_t slice = I / cl;
+  const size_t smem = q ? (size_t)slice * 2 : 0;
+  for (int64_t m0 = 0; m0 < M; m0 += 65535) {
+    const int64_t mc = (M - m0 < 65535) ? (M - m0) : 65535;
+    int rc;
+#define LLMQRT_RUN(T, V)                                                                                       \
+  rc = launch_row_kernel(silu_mul_kernel<T, V>, cl, mc, smem, st, reinterpret_cast<const T*>(gate_up) + m0 * ld, ld, \
+                         y ? reinterpret_cast<T*>(y) + m0 * I : (T*)nullptr, q ? q + m0 * I : (int8_t*)nullptr,   \
+                         scale_f32 ? scale_f32 + m0 : (float*)nullptr, I, slice)
+    if (dtype == LLMQRT_F16) { if (vec) LLMQRT_RUN(__half, true); else LLMQRT_RUN(__half, false); }
+    else { if (vec) LLMQRT_RUN(__nv_bfloat16, true); else LLMQRT_RUN(__nv_bfloat16, false); }
 #undef LLMQRT_RUN
-  return check_launch("silu_mul");
+    if (rc) return rc;
+    if (int rc2 = check_launch("silu_mul")) return rc2;
+  }
+  return LLMQRT_OK;
 }
 
 int llmqrt_rope_kv_write(void* q, int64_t q_token_stride, void* k, const void* v, int64_t kv_token_stride,
