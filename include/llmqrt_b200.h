@@ -108,6 +108,21 @@ int llmqrt_w8a8_int8_linear_per_channel(const int8_t* a, int64_t lda, const int8
                                         int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
                                         llmqrt_stream_t stream);
 
+/* Same operator as llmqrt_w8a8_int8_linear_per_channel for callers that cannot hand over a workspace
+ * because they are not allowed, or cannot afford, to allocate device memory: plug-ins of a server
+ * that owns the whole memory plan, or loops where the device-wide stall of cudaMalloc / cudaFree is
+ * unacceptable.  The split-K scratch is a fixed 8 MiB + 16 KiB array inside the library's device
+ * image (resident on every GPU that loads the library until the process exits); nothing is allocated
+ * or freed by the call.  Limits: M <= 64, N <= 524288, and the partial sums of the chosen split must
+ * fit in 8 MiB -- larger problems are rejected with LLMQRT_ERR_WORKSPACE.  The array is shared by all
+ * calls: calls that can overlap on one GPU race on it.  The first call on each device resolves the
+ * array's device address (cudaGetSymbolAddress) and should be made before any stream capture starts.
+ * No counterpart in the reference: it exists only for such callers. */
+int llmqrt_w8a8_int8_linear_per_channel_noalloc(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw,
+                                                const void* bias, int bias_dtype, const float* a_scale,
+                                                const float* w_scale, void* out, int out_dtype, int64_t ldo,
+                                                int64_t M, int64_t N, int64_t K, llmqrt_stream_t stream);
+
 /* Raw int32 accumulators acc[M, ldo] of the int8 GEMM (the quantity the parity gate checks bit for
  * bit); same kernels as the two entry points above with the epilogue reduced to a store. */
 int llmqrt_w8a8_int8_gemm_s32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldo,

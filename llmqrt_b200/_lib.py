@@ -41,6 +41,7 @@ _PROTOS = {
     "llmqrt_quantize_fp8_static": (c_int, [P, I32, I64, I64, I64, P, P, P]),
     "llmqrt_w8a8_int8_linear_per_tensor": (c_int, [P, I64, P, I64, P, F, P, F, P, I64, I64, I64, I64, P, P]),
     "llmqrt_w8a8_int8_linear_per_channel": (c_int, [P, I64, P, I64, P, I32, P, P, P, I32, I64, I64, I64, I64, P, P]),
+    "llmqrt_w8a8_int8_linear_per_channel_noalloc": (c_int, [P, I64, P, I64, P, I32, P, P, P, I32, I64, I64, I64, I64, P]),
     "llmqrt_w8a8_int8_gemm_s32": (c_int, [P, I64, P, I64, P, I64, I64, I64, I64, P, P]),
     "llmqrt_f8f8_tensorwise": (c_int, [P, I32, I64, P, I64, P, F, P, F, P, I32, I64, I64, I64, I64, P, P]),
     "llmqrt_f8f8bf16_rowwise": (c_int, [P, I32, I64, P, I64, P, I32, P, P, P, I64, I64, I64, I64, P, P]),
@@ -59,17 +60,32 @@ _PROTOS = {
 }
 
 EXPORTS = tuple(_PROTOS)
-_missing = []
-for _name, (_res, _args) in _PROTOS.items():
-    try:
-        _fn = getattr(_lib, _name)
-    except AttributeError:
-        _missing.append(_name)
-        continue
-    _fn.restype = _res
-    _fn.argtypes = _args
+
+
+def _bind(lib: ctypes.CDLL) -> list[str]:
+    missing = []
+    for name, (res, args) in _PROTOS.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            missing.append(name)
+            continue
+        fn.restype = res
+        fn.argtypes = args
+    return missing
+
+
+_missing = _bind(_lib)
 if _missing:
-    raise ImportError(f"{LIB_PATH} lacks symbols {_missing}; rebuild with `python -m llmqrt_b200.build --force`")
+    # A library built from older sources: rebuild once (needs nvcc) and load the fresh file.
+    import _ctypes
+    from . import build as _build
+    _ctypes.dlclose(_lib._handle)
+    _build.build()
+    _lib = ctypes.CDLL(LIB_PATH)
+    _missing = _bind(_lib)
+    if _missing:
+        raise ImportError(f"{LIB_PATH} lacks symbols {_missing}; rebuild with `python llmqrt_b200/build.py --force`")
 
 
 def last_error() -> str:

@@ -15,6 +15,8 @@
 // panel adds them in slice order (deterministic, exact for int32) and runs the epilogue.
 #include "gemm_w8a8.cuh"
 
+#include <mutex>
+
 namespace llmqrt {
 namespace {
 
@@ -212,3 +214,116 @@ int w8a8_gemm_stream(int kind, const uint8_t* A, int64_t lda, const uint8_t* W, 
 }
 
 }  // namespace llmqrt
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the per-channel int8 linear.
+//
+// Some hosts give a library nothing but the tensors of the call: an inference server that carves up
+// all device memory at start-up and forbids plug-ins to call cudaMalloc, or a decode loop that cannot
+// afford the device-wide synchronisation a cudaMalloc / cudaFree implies.  Such a caller has no way
+// to provide the split-K workspace the regular entry points expect.  This entry point therefore
+// carries its own scratch: a fixed array in the library's device data segment.  It costs
+// kNoAllocScratchBytes of device memory on every GPU that loads the library, for as long as the
+// process lives, and it bounds the problem size (see the error message below).
+//
+// The array is shared by every call and keeps whatever the previous call left in it.  The arrival
+// counters are therefore cleared on the stream at the start of each call; the partial sums need no
+// clearing because every slot that is read has been written by the same launch.  Two calls that may
+// run at the same time on one GPU (different streams without a dependency) would race on it.
+//
+// The device address of the array is looked up with cudaGetSymbolAddress the first time the entry
+// point runs on a device (the array's name is only a host-side handle, not a pointer a kernel could
+// use).  That first call should be made before any stream capture begins.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocCounterBytes = 16 * 1024;                    // 4096 row panels of 128 outputs
+constexpr size_t kNoAllocPartialBytes = (size_t)8 << 20;              // split-K partial sums
+constexpr size_t kNoAllocScratchBytes = kNoAllocCounterBytes + kNoAllocPartialBytes;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Device address of g_noalloc_scratch on the current device, resolved once per device.
+int noalloc_scratch(unsigned char** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static unsigned char* table[kMaxDevices] = {nullptr};
+  int dev = 0;
+  LLMQRT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return llmqrt::set_error(LLMQRT_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!table[dev]) {
+    void* p = nullptr;
+    LLMQRT_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));      // `dev` is the current device
+    table[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = table[dev];
+  return LLMQRT_OK;
+}
+
+template <int MB>
+int launch_noalloc(const uint8_t* A, int64_t lda, const uint8_t* W, int64_t ldw, int M, int N, int K,
+                   const llmqrt::Epilogue& epi, unsigned char* scratch, cudaStream_t st) {
+  using namespace llmqrt;
+  const int n_blocks = (int)ceil_div(N, kRowsPerBlock);
+  if ((size_t)n_blocks * sizeof(int) > kNoAllocCounterBytes)
+    return set_error(LLMQRT_ERR_WORKSPACE, "no-alloc int8 linear: N=%d exceeds the built-in scratch (max N = %d)", N,
+                     (int)(kNoAllocCounterBytes / sizeof(int)) * kRowsPerBlock);
+  // Same decomposition rule as the regular path, with the partial sums limited to the built-in array.
+  const int max_kps_smem = ((96 * 1024) / (MB * 8) - 64) / 64 * 64;
+  int want_splits = (int)ceil_div(3 * sm_count(), n_blocks);
+  int kps = (int)ceil_div(ceil_div(K, want_splits), 64) * 64;
+  if (kps < 256) kps = 256;
+  if (kps > max_kps_smem) kps = max_kps_smem;
+  if (kps > (int)ceil_div(K, 64) * 64) kps = (int)ceil_div(K, 64) * 64;
+  int splits = (int)ceil_div(K, kps);
+  while (splits > 1 && (size_t)splits * M * N * 4 > kNoAllocPartialBytes) {
+    kps += 64;
+    if (kps > max_kps_smem)
+      return set_error(LLMQRT_ERR_WORKSPACE,
+                       "no-alloc int8 linear: M=%d N=%d K=%d needs more than the %zu-byte built-in scratch; "
+                       "use llmqrt_w8a8_int8_linear_per_channel with a caller-provided workspace",
+                       M, N, K, kNoAllocPartialBytes);
+    splits = (int)ceil_div(K, kps);
+  }
+  int* counters = reinterpret_cast<int*>(scratch);
+  void* partials = scratch + kNoAllocCounterBytes;
+  if (splits > 1) LLMQRT_CUDA_OK(cudaMemsetAsync(counters, 0, (size_t)n_blocks * sizeof(int), st));
+  const size_t smem = (size_t)MB * 8 * xs_stride_for(kps);
+  auto kern = w8a8_stream_kernel<KIND_I8, MB>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;
+  kern<<<dim3(n_blocks, splits), kThreads, smem, st>>>(A, lda, W, ldw, M, N, K, kps, splits, partials, counters, epi);
+  return check_launch("w8a8_stream (no-alloc)");
+}
+
+}  // namespace
+
+extern "C" int llmqrt_w8a8_int8_linear_per_channel_noalloc(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw,
+                                                           const void* bias, int bias_dtype, const float* a_scale,
+                                                           const float* w_scale, void* out, int out_dtype, int64_t ldo,
+                                                           int64_t M, int64_t N, int64_t K, llmqrt_stream_t stream) {
+  using namespace llmqrt;
+  LLMQRT_REQUIRE(a && w && out && a_scale && w_scale, "no-alloc int8 linear: null pointer");
+  LLMQRT_REQUIRE(M >= 0 && N > 0 && K > 0 && N < (1ll << 31) && K < (1ll << 31), "no-alloc int8 linear: bad shape");
+  LLMQRT_REQUIRE(M <= 64, "no-alloc int8 linear: M=%lld exceeds the supported maximum of 64 rows", (long long)M);
+  LLMQRT_REQUIRE(K % 16 == 0 && lda >= K && ldw >= K && lda % 16 == 0 && ldw % 16 == 0 && ldo >= N,
+                 "no-alloc int8 linear: K and the leading dimensions must be multiples of 16 (K=%lld)", (long long)K);
+  LLMQRT_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                 "no-alloc int8 linear: operands must be 16-byte aligned");
+  LLMQRT_REQUIRE(out_dtype == LLMQRT_F16 || out_dtype == LLMQRT_BF16, "no-alloc int8 linear: out must be fp16/bf16");
+  LLMQRT_REQUIRE(!bias || bias_dtype == LLMQRT_F16 || bias_dtype == LLMQRT_BF16 || bias_dtype == LLMQRT_F32,
+                 "no-alloc int8 linear: bad bias dtype");
+  if (M == 0) return LLMQRT_OK;
+  unsigned char* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  Epilogue e{};
+  e.mode = EPI_COL_ROW; e.out_dtype = out_dtype; e.bias_dtype = bias_dtype; e.bias = bias; e.row_scale = a_scale;
+  e.col_scale = w_scale; e.out = out; e.ldo = ldo;
+  const uint8_t* A8 = reinterpret_cast<const uint8_t*>(a);
+  const uint8_t* W8 = reinterpret_cast<const uint8_t*>(w);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (M <= 8) return launch_noalloc<1>(A8, lda, W8, ldw, (int)M, (int)N, (int)K, e, scratch, st);
+  if (M <= 16) return launch_noalloc<2>(A8, lda, W8, ldw, (int)M, (int)N, (int)K, e, scratch, st);
+  if (M <= 32) return launch_noalloc<4>(A8, lda, W8, ldw, (int)M, (int)N, (int)K, e, scratch, st);
+  return launch_noalloc<8>(A8, lda, W8, ldw, (int)M, (int)N, (int)K, e, scratch, st);
+}
