@@ -1,0 +1,58 @@
+"""Worker of the tensor-parallel GPU test: one process per GPU, launched by torch.distributed.run.
+
+Builds the tiny decoder with tp = world size, runs prefill and a few CUDA-graph decode steps, gathers
+every rank's weight shard on rank 0 and compares the logits with the CPU oracle's emulation of the
+same sharding (per-rank activation scales, 16-bit partial sums added in rank order).
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    from llmqrt_b200.qwen2 import Qwen2Config, Qwen2Decoder
+    cfg = Qwen2Config.tiny()
+    B, S, steps, max_len = 3, 21, 3, 48
+    model = Qwen2Decoder(cfg, dev, batch=B, max_seq_len=max_len, tp=world, rank=rank, group=dist.group.WORLD, seed=5)
+    prompt = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(0))
+    nxt = model.prefill(prompt.to(dev))
+    logits, fed = [model.last_logits.clone()], []
+    for _ in range(steps):
+        fed.append(nxt.clone().cpu())
+        nxt = model.decode_step(nxt).clone()
+        logits.append(model.last_logits.clone())
+    # full-vocabulary logits: concatenate the vocabulary shards of all ranks
+    full = []
+    for lg in logits:
+        parts = [torch.empty_like(lg) for _ in range(world)]
+        dist.all_gather(parts, lg.contiguous())
+        full.append(torch.cat(parts, dim=1).cpu())
+    shards = [None] * world
+    dist.gather_object(model.export_shard(), shards if rank == 0 else None, dst=0)
+    ok = True
+    if rank == 0:
+        from oracle.qwen2 import Qwen2Oracle
+        orc = Qwen2Oracle(cfg, shards, B, max_len)
+        want = [orc.forward(prompt)] + [orc.forward(t.reshape(-1, 1)) for t in fed]
+        for got, w in zip(full, want):
+            err = float((got.double() - w.double()).norm() / w.double().norm())
+            print("rel_fro", err)
+            ok &= err < 2e-2
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, src=0)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
