@@ -352,8 +352,13 @@ def run_ours(args):
             line["cpu_baseline"], _ = cpu_baseline_sample(args)
         print(json.dumps(line))
     if world > 1:
+        # Tearing the NCCL communicator down while CUDA graphs that captured its collectives are alive
+        # blocks for ever; everything is measured and printed, so leave without the orderly shutdown.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -50,8 +50,12 @@ def main():
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, src=0)
     dist.barrier()
-    dist.destroy_process_group()
-    sys.exit(0 if int(flag.item()) == 1 else 1)
+    torch.cuda.synchronize(dev)
+    code = 0 if int(flag.item()) == 1 else 1
+    # destroy_process_group() blocks while CUDA graphs holding captured NCCL collectives are alive
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(code)
 
 
 if __name__ == "__main__":
