@@ -341,7 +341,10 @@ def run_ours(args):
             "gpu_launches": launches_per_step * K,
             "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel<int8> (TMA + tcgen05, weights as the M operand)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None,
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
+                         # dram read + write per launch, averaged over the four linears of a layer, from the ncu
+                         # capture summarised in profiles/gemm_tc_int8_decode_ncu_full.md (1 GPU, batch 64)
+                         "traffic": 60.0e6 if (world == 1 and B == 64) else None,
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": secs_per_launch * 1e6},
             "extras": {"launches_per_step": launches_per_step, "int8_gemm_by_shape": gemm_shapes,
                        "step_hbm_gbs": step_bytes / (secs / K) / 1e9, "step_hbm_frac": step_bytes / (secs / K) / 1e9 / peak,

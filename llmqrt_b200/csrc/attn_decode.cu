@@ -1,11 +1,12 @@
 // Decode attention over the contiguous GQA KV cache (one query token per sequence), split-KV.
 //
-// HBM-bound: every K and V row of every sequence is read exactly once, HBM -> registers with
-// 128-bit loads, and consumed by warp-level MMAs whose 16-row operand is the group of query heads
-// that share the KV head (GQA packing: up to 8 query heads per pass), so the arithmetic stays far
-// below the memory time.  No shared-memory staging of K/V:
-//   S = Q K^T : the K fragment of lane (g, t) is 16 contiguous bytes of key row g -- exactly what a
-//               coalesced load delivers; Q is pre-loaded with the same head_dim permutation.
+// HBM-bound: every K and V row of every sequence is read exactly once, streamed by cp.async through
+// a small per-warp ring in shared memory (three stages of 16 keys in flight per warp, no registers
+// held), and consumed by warp-level MMAs whose 16-row operand is the group of query heads that share
+// the KV head (GQA packing: up to 8 query heads per pass), so the arithmetic stays far below the
+// memory time.  Fragments are plain 16-byte pieces of rows, no transposes:
+//   S = Q K^T : the K fragment of lane (g, t) is 16 contiguous bytes of key row g; Q is pre-loaded
+//               with the same head_dim permutation.
 //   O += P V  : the V fragment needs two keys per register; two 16-byte loads (keys 2t, 2t+1) are
 //               interleaved with one byte-permute per register.  The MMA's n index is mapped to
 //               head_dim so that every load is a contiguous 128-byte row segment.
@@ -20,6 +21,16 @@ namespace {
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kRing = 3;            // cp.async stages per warp
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 lds_16B(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if constexpr (BF16) {
@@ -39,6 +50,8 @@ attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
                    int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
   constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
+  pdl_wait();
+  pdl_trigger();
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int rep = Hq / Hkv;
   const int L = seqlens[b];
@@ -74,24 +87,54 @@ attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   const uint16_t* vb = v_cache + (int64_t)b * cache_batch_stride + (int64_t)hkv * D;
   const float sl2 = scale * kLog2e;
 
-  for (int key0 = key_begin + warp * 16; key0 < key_end; key0 += kWarps * 16) {
-    // ---- issue all loads of this step ----
+  // Each warp streams its keys through a private ring of kRing stages in shared memory filled with
+  // cp.async (16 keys x (K row + V row) per stage), so several stages are in flight per warp without
+  // holding registers.  16-byte chunks are XOR-swizzled per row so that the fragment loads below
+  // (K: chunks 4j+t of rows g, g+1; V: chunk g+8h of rows 2t, 2t+2, ...) are bank-conflict free.
+  constexpr int ROWB = D * 2;                    // bytes of one K (or V) row of this head
+  constexpr int CPR = ROWB / 16;                 // 16-byte chunks per row
+  constexpr int STAGEB = 2 * 16 * ROWB;          // K tile + V tile
+  extern __shared__ __align__(16) uint8_t ring_all[];
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_all) + (uint32_t)(warp * kRing * STAGEB);
+  auto issue_stage = [&](int key0, int stage) {
+    if (key0 < key_end) {
+      const uint32_t base = ring + (uint32_t)(stage * STAGEB);
+#pragma unroll
+      for (int i = 0; i < 16 * CPR / 32; ++i) {
+        const int id = i * 32 + lane, r = id / CPR, c = id % CPR;
+        const int64_t row_off = (int64_t)min(key0 + r, key_end - 1) * cache_row_stride + c * 8;   // clamped rows are masked
+        cp_async_16(base + (uint32_t)(r * ROWB + ((c ^ ((r & 1) << 2)) << 4)), kb + row_off);
+        cp_async_16(base + (uint32_t)(16 * ROWB + r * ROWB + ((c ^ (((r >> 1) & 3) << 1)) << 4)), vb + row_off);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");          // always commit: group counting stays uniform
+  };
+  const int first_key = key_begin + warp * 16;
+#pragma unroll
+  for (int s = 0; s < kRing - 1; ++s) issue_stage(first_key + s * kWarps * 16, s);
+
+  int it = 0;
+  for (int key0 = first_key; key0 < key_end; key0 += kWarps * 16, ++it) {
+    issue_stage(key0 + (kRing - 1) * kWarps * 16, (it + kRing - 1) % kRing);
+    asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
+    __syncwarp();
+    const uint32_t st_base = ring + (uint32_t)((it % kRing) * STAGEB);
     uint4 kf[2][NJ];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
-      const int key = min(key0 + 8 * nb + g, key_end - 1);       // clamped rows are masked below
-      const uint16_t* kr = kb + (int64_t)key * cache_row_stride;
+      const int r = 8 * nb + g;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) kf[nb][j] = ldg_stream_16B(kr + 8 * (4 * j + t));
+      for (int j = 0; j < NJ; ++j) kf[nb][j] = lds_16B(st_base + (uint32_t)(r * ROWB + (((4 * j + t) ^ ((r & 1) << 2)) << 4)));
     }
     uint4 vf[4][NH];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const int key = min(key0 + 2 * t + (s & 1) + 8 * (s >> 1), key_end - 1);
-      const uint16_t* vr = vb + (int64_t)key * cache_row_stride;
+      const int r = 2 * t + (s & 1) + 8 * (s >> 1);
 #pragma unroll
-      for (int h = 0; h < NH; ++h) vf[s][h] = ldg_stream_16B(vr + 8 * (g + 8 * h));
+      for (int h = 0; h < NH; ++h)
+        vf[s][h] = lds_16B(st_base + (uint32_t)(16 * ROWB + r * ROWB + (((g + 8 * h) ^ (((r >> 1) & 3) << 1)) << 4)));
     }
+    __syncwarp();                                  // every lane has its fragments: the stage may be refilled
 
     // ---- S = Q K^T for 16 keys ----
     float s_acc[2][4];
@@ -162,7 +205,9 @@ attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   }
 
   // ---- merge the warps of this block ----
-  __shared__ float sm_o[kWarps][8][D];
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                                 // all rings are idle: reuse them for the merge
+  float (*sm_o)[8][D] = reinterpret_cast<float (*)[8][D]>(ring_all);
   __shared__ float sm_m[kWarps][8];
   __shared__ float sm_l[kWarps][8];
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -216,6 +261,8 @@ template <bool BF16, int D>
 __global__ void __launch_bounds__(D)
 attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int chunk,
                            int max_splits, const float* __restrict__ part_o, const float* __restrict__ part_ml) {
+  pdl_wait();
+  pdl_trigger();
   const int hq = blockIdx.x, b = blockIdx.y, dd = threadIdx.x;
   const int L = seqlens[b];
   const int n_splits = (L + chunk - 1) / chunk;
@@ -270,14 +317,21 @@ int launch_decode(const void* q, const void* kc, const void* vc, int64_t bs, int
     part_ml = part_o + (size_t)B * Hq * max_splits * D;
   }
   const float scale = 1.0f / sqrtf((float)D);
-  attn_decode_kernel<BF16, D><<<dim3(max_splits, Hkv, B), kThreads, 0, st>>>(
-      reinterpret_cast<const uint16_t*>(q), reinterpret_cast<const uint16_t*>(kc),
-      reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out), Hq, Hkv, chunk,
-      max_splits, scale, softcap, part_o, part_ml);
+  constexpr int smem = kWarps * kRing * 2 * 16 * D * 2;           // per-warp rings; also holds the 16 KiB merge tile
+  static_assert(smem >= kWarps * 8 * D * 4, "ring too small for the merge tile");
+  auto kern = attn_decode_kernel<BF16, D>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
+  if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
+                              reinterpret_cast<const uint16_t*>(q), reinterpret_cast<const uint16_t*>(kc),
+                              reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
+                              Hq, Hkv, chunk, max_splits, scale, softcap, part_o, part_ml))
+    return rc;
   if (int rc = check_launch("attn_decode")) return rc;
   if (max_splits > 1) {
-    attn_decode_combine_kernel<BF16, D><<<dim3(Hq, B), D, 0, st>>>(seqlens, reinterpret_cast<uint16_t*>(out), Hq,
-                                                                    chunk, max_splits, part_o, part_ml);
+    if (int rc = launch_chained(attn_decode_combine_kernel<BF16, D>, dim3(Hq, B), dim3(D), 0, st, 1, seqlens,
+                                reinterpret_cast<uint16_t*>(out), Hq, chunk, max_splits,
+                                static_cast<const float*>(part_o), static_cast<const float*>(part_ml)))
+      return rc;
     return check_launch("attn_decode_combine");
   }
   return LLMQRT_OK;

@@ -2,6 +2,7 @@
 #include "common.cuh"
 
 #include <atomic>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -45,10 +46,20 @@ int check_launch(const char* what) {
 
 long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("LLMQRT_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 int ensure_dynamic_smem(const void* func, int bytes) {
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, int> configured;
-  if (bytes <= 48 * 1024) return LLMQRT_OK;
+  // The 48 KiB a kernel gets without opting in covers static + dynamic shared memory together, so
+  // opt in from 32 KiB of dynamic memory on.
+  if (bytes <= 32 * 1024) return LLMQRT_OK;
   int dev = 0;
   LLMQRT_CUDA_OK(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> lock(mu);

@@ -53,6 +53,45 @@ int sm_count();  // cached multiprocessor count of the current device (capi.cu)
 int ensure_dynamic_smem(const void* func, int bytes);
 
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A decode step is a chain of several hundred short kernels; with
+// this launch attribute the blocks of the next kernel are scheduled, and run their set-up, while the
+// previous kernel drains.  Contract: a kernel launched through launch_chained() executes pdl_wait()
+// before its first access to global memory (it returns once the preceding kernel has completed and
+// its writes are visible) and may call pdl_trigger() as soon as it has started.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool pdl_enabled();   // capi.cu: on unless the environment variable LLMQRT_PDL is "0"
+
+template <typename... KArgs, typename... Args>
+inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_x,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+  return LLMQRT_OK;
+}
+
+// ----------------------------------------------------------------------------------------------
 // 16-bit float helpers.  T is __half or __nv_bfloat16.
 // ----------------------------------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);

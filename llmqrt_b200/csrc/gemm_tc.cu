@@ -301,6 +301,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   if (threadIdx.x == 0) TC_TRACE(1);
+  // Everything above touched only shared and tensor memory; from here on global memory is read.
+  pdl_wait();
+  pdl_trigger();
 
   // Work items: split mode -> exactly one tile per cluster (grid = tiles * S, non persistent);
   // otherwise a persistent walk over the tiles.
@@ -591,6 +594,11 @@ cudaLaunchConfig_t make_config(int grid, int cluster, cudaStream_t st, cudaLaunc
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (pdl_enabled()) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   return cfg;
 }
 
@@ -607,7 +615,7 @@ int max_active_clusters(int cluster) {
   auto kern = gemm_tc_kernel<KIND, BN>;
   int n = 0;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>()) == LLMQRT_OK) {
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cudaLaunchConfig_t cfg = make_config<KIND, BN>(cluster, cluster, nullptr, attr);
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
       cudaGetLastError();
@@ -641,7 +649,7 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaS
   }
   prm.splits = splits;
   const int grid = splits > 1 ? tiles * splits : (tiles < sms ? tiles : sms);
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cudaLaunchConfig_t cfg = make_config<KIND, BN>(grid, splits, st, attr);
   LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_p, tm_q, prm));
   return check_launch("gemm_tc");

@@ -107,6 +107,8 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __res
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_ss, slot_amax;
+  pdl_wait();
+  pdl_trigger();
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -159,6 +161,8 @@ silu_mul_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, in
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_amax;
+  pdl_wait();
+  pdl_trigger();
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -200,20 +204,7 @@ int pick_cluster(int64_t M, int64_t row_len) {
 template <typename Kern, typename... Args>
 int launch_row_kernel(Kern kern, int cl, int64_t M, size_t smem, cudaStream_t st, Args... args) {
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem)) return rc;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)cl, (unsigned)M, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)cl;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, args...));
-  return LLMQRT_OK;
+  return launch_chained(kern, dim3((unsigned)cl, (unsigned)M, 1), dim3(kThreads, 1, 1), smem, st, cl, args...);
 }
 
 // One block per (token, head); thread i rotates the pair (i, i + d/2).
@@ -223,6 +214,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ q, int64_t q_token_stride, 
                                      T* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
                                      int pos0, const int32_t* __restrict__ pos_dev, const float* __restrict__ cos_tab,
                                      const float* __restrict__ sin_tab, int table_rows, int S, int Hq, int Hkv, int d) {
+  pdl_wait();
+  pdl_trigger();
   const int token = blockIdx.x, head = blockIdx.y;
   const int b = token / S, s = token - b * S;
   const int pos = (pos_dev ? *pos_dev : pos0) + s;
@@ -338,12 +331,14 @@ int llmqrt_rope_kv_write(void* q, int64_t q_token_stride, void* k, const void* v
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)(B * S), (unsigned)(Hq + Hkv));
 #define LLMQRT_RUN(T)                                                                                               \
-  rope_kv_write_kernel<T><<<grid, (unsigned)(d / 2), 0, st>>>(                                                      \
+  rc = launch_chained(rope_kv_write_kernel<T>, grid, dim3((unsigned)(d / 2)), 0, st, 1,                              \
       reinterpret_cast<T*>(q), q_token_stride, reinterpret_cast<T*>(k), reinterpret_cast<const T*>(v),              \
       kv_token_stride, reinterpret_cast<T*>(k_cache), reinterpret_cast<T*>(v_cache), cache_batch_stride,           \
-      cache_row_stride, pos0, pos_dev, cos_table, sin_table, (int)table_rows, (int)S, (int)Hq, (int)Hkv, (int)d)
+      cache_row_stride, (int)pos0, pos_dev, cos_table, sin_table, (int)table_rows, (int)S, (int)Hq, (int)Hkv, (int)d)
+  int rc;
   if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
 #undef LLMQRT_RUN
+  if (rc) return rc;
   return check_launch("rope_kv_write");
 }
 

@@ -98,6 +98,8 @@ template <typename T, bool FP8>
 __global__ void __launch_bounds__(kThreads)
 quantize_per_token_kernel(const T* __restrict__ x, int64_t K, int64_t ldx, uint8_t* __restrict__ q,
                           T* __restrict__ scale_x, float* __restrict__ scale_f32, float scale_mul, bool vec_ok) {
+  pdl_wait();
+  pdl_trigger();
   const int64_t m = blockIdx.x;
   const T* row = x + m * ldx;
   float amax = block_max(row_absmax<T>(row, K, vec_ok));
@@ -156,8 +158,9 @@ int launch(const void* x, int64_t M, int64_t K, int64_t ldx, int per_token, uint
     return check_launch("quantize_static");
   }
   if (per_token) {
-    quantize_per_token_kernel<T, FP8><<<(unsigned)M, kThreads, 0, st>>>(xp, K, ldx, q, reinterpret_cast<T*>(scale_x),
-                                                                       scale_f32, scale_mul, vec_ok);
+    if (int rc = launch_chained(quantize_per_token_kernel<T, FP8>, dim3((unsigned)M), dim3(kThreads), 0, st, 1, xp, K,
+                                ldx, q, reinterpret_cast<T*>(scale_x), scale_f32, scale_mul, vec_ok))
+      return rc;
     return check_launch("quantize_per_token");
   }
   if (!workspace) return set_error(LLMQRT_ERR_WORKSPACE, "per-tensor quantization needs the workspace");
