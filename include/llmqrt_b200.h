@@ -201,12 +201,20 @@ int llmqrt_kv_append(void* k_cache, void* v_cache, int64_t cache_batch_stride, i
                      int64_t B, int64_t S_new, int64_t Hkv, int64_t d, int64_t Smax, llmqrt_stream_t stream);
 
 /* Decode attention: q [B, Hq, d] (one new token per sequence) attends to cache rows
- * [0, seqlens[b]) of sequence b; out [B, Hq, d].  softcap = 0 disables logit soft-capping.
- * ref: flash_attn_with_kvcache call site, runtime/nn_models/modules/nonlinear/attn.py:300-315. */
-int llmqrt_attn_decode(const void* q, const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
-                       int64_t cache_row_stride, const int32_t* seqlens, void* out, int dtype, int64_t B, int64_t Hq,
-                       int64_t Hkv, int64_t d, int64_t max_seqlen, float softcap, void* workspace,
-                       llmqrt_stream_t stream);
+ * [0, seqlens[b]) of sequence b; out [B, Hq, d] contiguous.  softcap = 0 disables logit soft-capping.
+ * q_batch_stride = elements between the query rows of consecutive sequences (heads and d contiguous),
+ * so q may be a slice of a fused qkv projection output.
+ * out_q / out_scale (both or neither; may be NULL): additionally the per-token int8 quantization of
+ * out viewed as [B, Hq * d] -- the same arithmetic as llmqrt_quantize_int8(per_token = 1) applied to
+ * out, scales as fp32 -- which is the input of an int8 output projection (Hq * d <= 8192).
+ * ref: flash_attn_with_kvcache call site, runtime/nn_models/modules/nonlinear/attn.py:300-315;
+ *      the quantization that follows it in an int8 model: quantize_activation_per_token_absmax,
+ *      runtime/nn_models/modules/linear/linear_sq.py:56-65, called from
+ *      SqW8A8BBF16OBF16PerChannel.forward, linear_sq.py:185. */
+int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                       int64_t cache_batch_stride, int64_t cache_row_stride, const int32_t* seqlens, void* out,
+                       int8_t* out_q, float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
+                       int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream);
 
 /* Prefill attention over the new tokens: q [B, S, Hq, d], k / v [B, S, Hkv, d], out [B, S, Hq, d],
  * token stride given in elements (heads and d contiguous), causal mask optional.

@@ -51,7 +51,7 @@ _PROTOS = {
     "llmqrt_awq_dequantize_t": (c_int, [P, P, I64, I64, I64, P, P]),
     "llmqrt_gemm_16bit": (c_int, [P, I64, P, I64, P, P, I64, I32, I64, I64, I64, P, P]),
     "llmqrt_kv_append": (c_int, [P, P, I64, I64, P, P, P, c_int32, I32, I64, I64, I64, I64, I64, P]),
-    "llmqrt_attn_decode": (c_int, [P, P, P, I64, I64, P, P, I32, I64, I64, I64, I64, I64, F, P, P]),
+    "llmqrt_attn_decode": (c_int, [P, I64, P, P, I64, I64, P, P, P, P, I32, I64, I64, I64, I64, I64, F, P, P]),
     "llmqrt_attn_prefill": (c_int, [P, I64, P, P, I64, P, I64, I32, I64, I64, I64, I64, I64, I32, F, P]),
     "llmqrt_rmsnorm": (c_int, [P, P, P, P, F, P, P, P, I32, I64, I64, P]),
     "llmqrt_rope_kv_write": (c_int, [P, I64, P, P, I64, P, P, I64, I64, c_int32, P, P, P, I64, I32, I64, I64, I64,
@@ -75,7 +75,11 @@ def _bind(lib: ctypes.CDLL) -> list[str]:
     return missing
 
 
+ABI_VERSION = 2          # llmqrt_abi_version() of the sources these prototypes describe
+
 _missing = _bind(_lib)
+if not _missing and _lib.llmqrt_abi_version() != ABI_VERSION:
+    _missing = ["llmqrt_abi_version == %d" % ABI_VERSION]
 if _missing:
     # A library built from older sources: rebuild once (needs nvcc) and load the fresh file.
     import _ctypes
@@ -84,6 +88,8 @@ if _missing:
     _build.build()
     _lib = ctypes.CDLL(LIB_PATH)
     _missing = _bind(_lib)
+    if not _missing and _lib.llmqrt_abi_version() != ABI_VERSION:
+        _missing = ["llmqrt_abi_version == %d" % ABI_VERSION]
     if _missing:
         raise ImportError(f"{LIB_PATH} lacks symbols {_missing}; rebuild with `python llmqrt_b200/build.py --force`")
 

@@ -72,8 +72,13 @@ def kv_append(k_cache, v_cache, k, v, cache_seqlens=None, start_pos: int = 0):
                L.dtype_code(k_cache.dtype), B, S_new, Hkv, d, k_cache.shape[1], L.stream(dev))
 
 
-def attn_decode(q, k_cache, v_cache, seqlens, max_seqlen: int, softcap: float = 0.0):
-    """q [B, Hq, d] attends to rows [0, seqlens[b]) of the caches [Bc, Smax, Hkv, d]; returns [B, Hq, d]."""
+def attn_decode(q, k_cache, v_cache, seqlens, max_seqlen: int, softcap: float = 0.0, quantize: bool = False):
+    """q [B, Hq, d] attends to rows [0, seqlens[b]) of the caches [Bc, Smax, Hkv, d]; returns [B, Hq, d].
+
+    q may be a slice of a fused projection output (any batch stride, heads and d contiguous).
+    quantize=True returns (out, out_q int8 [B, Hq*d], scale fp32 [B]): the per-token int8
+    quantization of out, computed by the kernel that merges the KV splits.
+    """
     dev = L.require_cuda(q, k_cache, v_cache, seqlens)
     B, Hq, d = q.shape
     Hkv = k_cache.shape[2]
@@ -83,13 +88,18 @@ def attn_decode(q, k_cache, v_cache, seqlens, max_seqlen: int, softcap: float = 
         raise TypeError("attn_decode: q and the caches must share one dtype")
     if seqlens.dtype != torch.int32:
         raise TypeError("attn_decode: seqlens must be int32")
-    q = q.contiguous()
-    out = torch.empty_like(q)
+    if B > 0 and (q.stride(2) != 1 or q.stride(1) != d or (B > 1 and (q.stride(0) < Hq * d or q.stride(0) % 8))
+                  or q.data_ptr() % 16):
+        q = q.contiguous()
+    out = torch.empty((B, Hq, d), dtype=q.dtype, device=dev)
+    out_q = torch.empty((B, Hq * d), dtype=torch.int8, device=dev) if quantize else None
+    scale = torch.empty((B,), dtype=torch.float32, device=dev) if quantize else None
+    q_stride = q.stride(0) if B > 1 else Hq * d
     with torch.cuda.device(dev):
-        L.call("llmqrt_attn_decode", L.ptr(q), L.ptr(k_cache), L.ptr(v_cache), k_cache.stride(0), k_cache.stride(1),
-               L.ptr(seqlens), L.ptr(out), L.dtype_code(q.dtype), B, Hq, Hkv, d, int(max_seqlen), float(softcap),
-               L.ptr(L.workspace(dev)), L.stream(dev))
-    return out
+        L.call("llmqrt_attn_decode", L.ptr(q), q_stride, L.ptr(k_cache), L.ptr(v_cache), k_cache.stride(0),
+               k_cache.stride(1), L.ptr(seqlens), L.ptr(out), L.ptr(out_q), L.ptr(scale), L.dtype_code(q.dtype), B, Hq,
+               Hkv, d, int(max_seqlen), float(softcap), L.ptr(L.workspace(dev)), L.stream(dev))
+    return (out, out_q, scale) if quantize else out
 
 
 def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None, rotary_sin=None,

@@ -12,7 +12,10 @@
 //               head_dim so that every load is a contiguous 128-byte row segment.
 // Grid (splits, Hkv, B); each block walks `chunk` keys with 4 warps (16 keys per warp step), merges
 // its warps through shared memory and writes either the final output (single split) or an
-// unnormalised partial (max, sum, O) that a small combine kernel reduces.
+// unnormalised partial (max, sum, O) that a small combine kernel reduces; the combine kernel can also
+// emit the per-token int8 quantization of the result, which is what an int8 output projection reads.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace llmqrt {
@@ -44,7 +47,7 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b)
 
 template <bool BF16, int D>
 __global__ void __launch_bounds__(kThreads)
-attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
+attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const uint16_t* __restrict__ k_cache,
                    const uint16_t* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
                    const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int Hkv, int chunk,
                    int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml) {
@@ -65,7 +68,7 @@ attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   // ---- Q fragments: head row g (zero when g >= rep), same chunk order as the K loads ----
   uint32_t qf[NJ][4];
   {
-    const uint16_t* qrow = q + ((int64_t)b * Hq + hkv * rep + g) * D;
+    const uint16_t* qrow = q + (int64_t)b * q_batch_stride + (int64_t)(hkv * rep + g) * D;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
       uint4 v = make_uint4(0, 0, 0, 0);
@@ -257,30 +260,77 @@ attn_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   }
 }
 
+// Merges the split partials of one sequence (all heads) and, optionally, quantizes the merged token
+// row to int8 with a per-token scale -- the arithmetic of the stand-alone per-token quantizer applied
+// to the 16-bit result.  One block per sequence, eight consecutive elements of a head per thread.
+// With out_q the whole row must sit in one pass of the block (Hq * D / 8 <= blockDim.x).
 template <bool BF16, int D>
-__global__ void __launch_bounds__(D)
+__global__ void __launch_bounds__(1024)
 attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int chunk,
-                           int max_splits, const float* __restrict__ part_o, const float* __restrict__ part_ml) {
-  pdl_wait();
-  pdl_trigger();
-  const int hq = blockIdx.x, b = blockIdx.y, dd = threadIdx.x;
+                           int max_splits, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                           int8_t* __restrict__ out_q, float* __restrict__ out_scale) {
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  __shared__ float red[32];
+  pdl_trigger_then_wait();
+  const int b = blockIdx.x;
   const int L = seqlens[b];
   const int n_splits = (L + chunk - 1) / chunk;
-  if (n_splits <= 1) return;                       // the main kernel already wrote the result
-  const int64_t base = ((int64_t)b * Hq + hq) * max_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float lsum = 0.f, osum = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float f = exp2f(part_ml[(base + s) * 2] - M);
-    lsum += part_ml[(base + s) * 2 + 1] * f;
-    osum += part_o[(base + s) * D + dd] * f;
+  if (n_splits <= 1 && !out_q) return;             // the main kernel already wrote the result
+  const int units = Hq * D / 8;
+  uint16_t* orow = out + (int64_t)b * Hq * D;
+  float amax = 0.f;
+  float val[8];
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    __align__(16) T e[8];
+    if (n_splits <= 1) {
+      *reinterpret_cast<uint4*>(e) = *reinterpret_cast<const uint4*>(orow + u * 8);
+    } else {
+      const int hq = (u * 8) / D, dd = (u * 8) % D;
+      const int64_t base = ((int64_t)b * Hq + hq) * max_splits;
+      float M = -INFINITY;
+      for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+      float lsum = 0.f, osum[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) osum[j] = 0.f;
+      for (int s = 0; s < n_splits; ++s) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+        const float f = exp2f(ml.x - M);
+        lsum += ml.y * f;
+        const float4 a = *reinterpret_cast<const float4*>(part_o + (base + s) * D + dd);
+        const float4 c = *reinterpret_cast<const float4*>(part_o + (base + s) * D + dd + 4);
+        osum[0] += a.x * f; osum[1] += a.y * f; osum[2] += a.z * f; osum[3] += a.w * f;
+        osum[4] += c.x * f; osum[5] += c.y * f; osum[6] += c.z * f; osum[7] += c.w * f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(lsum > 0.f ? osum[j] / lsum : 0.f);
+      *reinterpret_cast<uint4*>(orow + u * 8) = *reinterpret_cast<const uint4*>(e);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      val[j] = to_f32<T>(e[j]);
+      amax = fmaxf(amax, fabsf(val[j]));
+    }
   }
-  const float r = lsum > 0.f ? osum / lsum : 0.f;
-  uint16_t bits;
-  if constexpr (BF16) { __nv_bfloat16 hv = __float2bfloat16_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
-  else { __half hv = __float2half_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
-  out[((int64_t)b * Hq + hq) * D + dd] = bits;
+  if (!out_q) return;
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+  float s = round_to<T>(fmaxf(amax, 1e-5f));
+  s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
+  if (threadIdx.x == 0) out_scale[b] = s;
+  const int u = threadIdx.x;
+  if (u < units) {
+    __align__(8) int8_t o8[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = rintf(round_to<T>(__fdiv_rn(val[j], s)));
+      v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
+      o8[j] = (int8_t)(int)v;
+    }
+    *reinterpret_cast<uint2*>(out_q + (int64_t)b * Hq * D + u * 8) = *reinterpret_cast<const uint2*>(o8);
+  }
 }
 
 __global__ void kv_append_kernel(uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, int64_t batch_stride16,
@@ -299,8 +349,9 @@ __global__ void kv_append_kernel(uint4* __restrict__ k_cache, uint4* __restrict_
 }
 
 template <bool BF16, int D>
-int launch_decode(const void* q, const void* kc, const void* vc, int64_t bs, int64_t rs, const int32_t* seqlens,
-                  void* out, int B, int Hq, int Hkv, int max_seqlen, float softcap, void* workspace, cudaStream_t st) {
+int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, int64_t bs, int64_t rs,
+                  const int32_t* seqlens, void* out, int8_t* out_q, float* out_scale, int B, int Hq, int Hkv,
+                  int max_seqlen, float softcap, void* workspace, cudaStream_t st) {
   // keys per block: 256, halved while the grid would not cover the SMs twice
   int chunk = 256;
   while (chunk > 64 && (int64_t)B * Hkv * ceil_div(max_seqlen, chunk) < 2 * sm_count()) chunk /= 2;
@@ -322,15 +373,18 @@ int launch_decode(const void* q, const void* kc, const void* vc, int64_t bs, int
   auto kern = attn_decode_kernel<BF16, D>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
   if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
-                              reinterpret_cast<const uint16_t*>(q), reinterpret_cast<const uint16_t*>(kc),
+                              reinterpret_cast<const uint16_t*>(q), qbs, reinterpret_cast<const uint16_t*>(kc),
                               reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
                               Hq, Hkv, chunk, max_splits, scale, softcap, part_o, part_ml))
     return rc;
   if (int rc = check_launch("attn_decode")) return rc;
-  if (max_splits > 1) {
-    if (int rc = launch_chained(attn_decode_combine_kernel<BF16, D>, dim3(Hq, B), dim3(D), 0, st, 1, seqlens,
+  if (max_splits > 1 || out_q) {
+    const int units = Hq * D / 8;
+    const int threads = units >= 1024 ? 1024 : (units + 31) / 32 * 32;
+    if (int rc = launch_chained(attn_decode_combine_kernel<BF16, D>, dim3(B), dim3(threads), 0, st, 1, seqlens,
                                 reinterpret_cast<uint16_t*>(out), Hq, chunk, max_splits,
-                                static_cast<const float*>(part_o), static_cast<const float*>(part_ml)))
+                                static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out_q,
+                                out_scale))
       return rc;
     return check_launch("attn_decode_combine");
   }
@@ -363,24 +417,28 @@ int llmqrt_kv_append(void* k_cache, void* v_cache, int64_t cache_batch_stride, i
   return check_launch("kv_append");
 }
 
-int llmqrt_attn_decode(const void* q, const void* k_cache, const void* v_cache, int64_t cache_batch_stride,
-                       int64_t cache_row_stride, const int32_t* seqlens, void* out, int dtype, int64_t B, int64_t Hq,
-                       int64_t Hkv, int64_t d, int64_t max_seqlen, float softcap, void* workspace,
-                       llmqrt_stream_t stream) {
+int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                       int64_t cache_batch_stride, int64_t cache_row_stride, const int32_t* seqlens, void* out,
+                       int8_t* out_q, float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
+                       int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream) {
   LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "attn_decode: dtype must be fp16 or bf16");
   LLMQRT_REQUIRE(d == 64 || d == 128, "attn_decode: head_dim must be 64 or 128 (got %lld)", (long long)d);
   LLMQRT_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8, "attn_decode: need Hq %% Hkv == 0 and at most 8 query heads per KV head");
   LLMQRT_REQUIRE(B >= 0 && B < 65536 && Hkv < 65536 && max_seqlen >= 0, "attn_decode: bad shape");
   LLMQRT_REQUIRE(cache_batch_stride % 8 == 0 && cache_row_stride % 8 == 0, "attn_decode: cache strides must be multiples of 8");
+  LLMQRT_REQUIRE(q_batch_stride >= Hq * d && q_batch_stride % 8 == 0, "attn_decode: q_batch_stride must be a multiple of 8 and at least Hq * d");
+  LLMQRT_REQUIRE(!out_q || (out_scale && Hq * d <= 8192), "attn_decode: quantized output needs out_scale and Hq * d <= 8192");
   if (B == 0) return LLMQRT_OK;
   LLMQRT_REQUIRE(q && k_cache && v_cache && seqlens && out, "attn_decode: null pointer");
   LLMQRT_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
-                   reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0, "attn_decode: pointers must be 16-byte aligned");
+                   reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(out_q) & 7) == 0, "attn_decode: pointers must be 16-byte aligned (out_q: 8)");
   cudaStream_t st = (cudaStream_t)stream;
   const bool bf = dtype == LLMQRT_BF16;
 #define LLMQRT_GO(BF, DD)                                                                                          \
-  return launch_decode<BF, DD>(q, k_cache, v_cache, cache_batch_stride, cache_row_stride, seqlens, out, (int)B,    \
-                               (int)Hq, (int)Hkv, (int)max_seqlen, softcap, workspace, st)
+  return launch_decode<BF, DD>(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, cache_row_stride, seqlens, \
+                               out, out_q, out_scale, (int)B, (int)Hq, (int)Hkv, (int)max_seqlen, softcap,         \
+                               workspace, st)
   if (d == 128) { if (bf) LLMQRT_GO(true, 128); else LLMQRT_GO(false, 128); }
   if (bf) LLMQRT_GO(true, 64); else LLMQRT_GO(false, 64);
 #undef LLMQRT_GO

@@ -61,6 +61,14 @@ int ensure_dynamic_smem(const void* func, int bytes);
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Entry of a kernel whose successor is typically a GEMM: the successor may start (and request its
+// weights, which nobody in the chain writes) while this kernel is still waiting for its own
+// predecessor.  Safe because every chained kernel waits before it reads or writes anything else, and
+// a wait only returns after the predecessor, hence the predecessor's predecessor, has completed.
+__device__ __forceinline__ void pdl_trigger_then_wait() {
+  pdl_trigger();
+  pdl_wait();
+}
 bool pdl_enabled();   // capi.cu: on unless the environment variable LLMQRT_PDL is "0"
 
 template <typename... KArgs, typename... Args>

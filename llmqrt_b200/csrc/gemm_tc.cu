@@ -253,8 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   constexpr int kStages = num_stages<BN>();
   constexpr int kStageBytes = stage_bytes<BN>();
   constexpr uint32_t kTmemCols = tmem_cols<BN>();
-  constexpr int kBurst = kStages >= 8 ? 4 : (kStages >= 4 ? 2 : 1);
-  static_assert(BN > 128 || kStages * kStageBytes >= 2 * kBM * BN * 4, "ring too small for the reduce buffers");
+  constexpr int kBurst = kStages >= 8 ? 4 : (kStages >= 4 ? 2 : 1);  static_assert(BN > 128 || kStages * kStageBytes >= 2 * kBM * BN * 4, "ring too small for the reduce buffers");
   static_assert(kStages >= 3, "pipeline too shallow");
 
   extern __shared__ uint8_t smem_raw[];
@@ -302,8 +301,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   const uint32_t tmem_base = tmem_base_slot;
   if (threadIdx.x == 0) TC_TRACE(1);
   // Everything above touched only shared and tensor memory; from here on global memory is read.
-  pdl_wait();
-  pdl_trigger();
+  // The producer thread waits later: it first requests weight tiles, which the preceding kernel of
+  // the stream does not write.
+  if (threadIdx.x != 0) {
+    pdl_wait();
+    pdl_trigger();
+  }
 
   // Work items: split mode -> exactly one tile per cluster (grid = tiles * S, non persistent);
   // otherwise a persistent walk over the tiles.
@@ -321,6 +324,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       int issued = 0;
+      // x coordinate in ELEMENTS of the tensor map's type; the maps are built on bytes for the
+      // 8-bit kinds and on 16-bit elements for fp16/bf16.
+      constexpr int kXPerBlock = KIND == tc::MMA_F16 ? kRowBytes / 2 : kRowBytes;
+      // The weight operand is a constant of the model, so the first ring-full of weight tiles of the
+      // first work item is requested BEFORE waiting for the preceding kernel of the stream; the
+      // activation tiles of the same stages follow after the wait and complete the same barriers.
+      // On a programmatic launch this streams up to a ring of weights per SM while the preceding
+      // kernel is still running.
+      const int pre = first_tile < num_tiles ? min(kStages, kb_count) : 0;
+      for (int phase_w = 1; phase_w >= 0; --phase_w) {     // 1: weights, 0: activations
+        const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
+        const int rot = pre ? (tp * 5 + tq * 3) % kb_count : 0;
+        const bool load_p = (prm.swap != 0) == (phase_w != 0);
+        for (int g = 0; g < pre; ++g) {
+          int kr = g + rot;
+          if (kr >= kb_count) kr -= kb_count;
+          const int x = (kb_begin + kr) * kXPerBlock;
+          const uint32_t full = tc::smem_u32(&bar_full[g]);
+          uint8_t* sp = tiles + g * kStageBytes;
+          if (phase_w) tc::mbar_arrive_expect_tx(full, kStageBytes);
+          if (load_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
+          else tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
+        }
+        if (phase_w) {
+          // (Prefetching further weight tiles into L2 here was measured to slow the kernel down: the
+          // ring already keeps more bytes in flight than HBM needs, and the activation loads then
+          // queue behind the prefetches.)
+          pdl_wait();
+          pdl_trigger();
+        }
+      }
+      issued = pre;
+      if (pre == kStages) phase = 1; else stage_i = pre;
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
         // Blocks start at different K offsets so that they do not all pull the same activation rows
@@ -329,7 +365,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         // K blocks are issued in bursts of kBurst consecutive blocks: the same weight rows are then
         // requested at consecutive 128-byte offsets within nanoseconds, which the DRAM controller can
         // serve from open pages (a lone 128-byte piece per row and visit is the worst case for HBM).
-        for (int it0 = 0; it0 < kb_count && ok; it0 += kBurst) {
+        for (int it0 = tile == first_tile ? pre : 0; it0 < kb_count && ok; it0 += kBurst) {
           const int nb = min(kBurst, kb_count - it0);
           int s_w = stage_i;
           uint32_t ph_w = phase;
@@ -345,9 +381,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
             const uint32_t full = tc::smem_u32(&bar_full[stage_i]);
             uint8_t* sp = tiles + stage_i * kStageBytes;
             tc::mbar_arrive_expect_tx(full, kStageBytes);
-            // x coordinate in ELEMENTS of the tensor map's type; the maps are built on bytes for the
-            // 8-bit kinds and on 16-bit elements for fp16/bf16.
-            const int x = kb * (KIND == tc::MMA_F16 ? kRowBytes / 2 : kRowBytes);
+            const int x = kb * kXPerBlock;
             tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
             tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
             ++issued;

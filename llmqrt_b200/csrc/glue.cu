@@ -107,8 +107,7 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __res
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_ss, slot_amax;
-  pdl_wait();
-  pdl_trigger();
+  pdl_trigger_then_wait();
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -161,8 +160,7 @@ silu_mul_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, in
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_amax;
-  pdl_wait();
-  pdl_trigger();
+  pdl_trigger_then_wait();
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -191,6 +189,85 @@ silu_mul_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, in
     quantize_slice_int8<T, VEC>(row, units, amax, q + m * I + c0, rank == 0 ? scale_f32 + m : nullptr);
   }
   if (cl > 1) cg::this_cluster().sync();
+}
+
+// Block-wide reduction for a block of any whole number of warps (up to 32).
+template <bool IS_MAX>
+__device__ __forceinline__ float block_reduce_any(float v) {
+  __shared__ float red[32];
+  __shared__ float result;
+  const int nwarps = blockDim.x >> 5;
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float w = (int)threadIdx.x < nwarps ? red[threadIdx.x] : 0.f;
+    w = IS_MAX ? warp_max(w) : warp_sum(w);
+    if (threadIdx.x == 0) result = w;
+  }
+  __syncthreads();
+  return result;
+}
+
+// RMSNorm for rows of up to 8192 elements: one block per row, eight elements per thread held in
+// registers from the load to the quantized store (no staging, two block reductions).
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ x_out,
+                    const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
+                    float* __restrict__ scale_f32, int64_t H) {
+  pdl_trigger_then_wait();
+  const int64_t m = blockIdx.x, u = threadIdx.x;
+  const bool on = u * 8 < H;
+  const int64_t off = m * H;
+  T e[8], w[8];
+  float f[8];
+  float ss = 0.f;
+  if (on) {
+    T r[8];
+    load_unit<T, true>(x + off, u, e);
+    if (residual) load_unit<T, true>(residual + off, u, r);
+    load_unit<T, true>(weight, u, w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = to_f32<T>(e[j]);
+      if (residual) v = round_to<T>(v + to_f32<T>(r[j]));                 // h = x + r in T
+      e[j] = from_f32<T>(v);
+      f[j] = v;
+      ss += v * v;
+    }
+    if (x_out) store_unit<T, true>(x_out + off, u, e);
+  }
+  ss = block_reduce_any<false>(ss);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  float amax = 0.f;
+  if (on) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float n = round_to<T>(f[j] * inv);                            // (x32 * inv).to(T)
+      f[j] = round_to<T>(to_f32<T>(w[j]) * n);                            // weight * that, in T
+      e[j] = from_f32<T>(f[j]);
+      amax = fmaxf(amax, fabsf(f[j]));
+    }
+    if (y) store_unit<T, true>(y + off, u, e);
+  }
+  if (q) {
+    amax = block_reduce_any<true>(amax);
+    float s = round_to<T>(fmaxf(amax, 1e-5f));
+    s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
+    if (threadIdx.x == 0) scale_f32[m] = s;
+    if (on) {
+      __align__(8) int8_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = rintf(round_to<T>(__fdiv_rn(f[j], s)));
+        v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
+        o[j] = (int8_t)(int)v;
+      }
+      *reinterpret_cast<uint2*>(q + off + u * 8) = *reinterpret_cast<const uint2*>(o);
+    }
+  }
 }
 
 // Cluster size for a row kernel: as many CTAs per row as needed to put about two CTAs on every SM,
@@ -264,6 +341,20 @@ int llmqrt_rmsnorm(const void* x, const void* residual, void* x_out, const void*
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = H % 8 == 0 && aligned16(x) && aligned16(residual) && aligned16(x_out) && aligned16(weight) &&
                    aligned16(y) && (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+  if (vec && H <= 8192 && M <= 0x7fffffffll) {
+    // the row fits the registers of one block: one block per row, rows on gridDim.x
+    const unsigned threads = (unsigned)(((H / 8) + 31) / 32 * 32);
+    int rc;
+#define LLMQRT_RUN(T)                                                                                             \
+  rc = launch_chained(rmsnorm_regs_kernel<T>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0, st, 1,               \
+                      reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(residual),                          \
+                      reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), eps, reinterpret_cast<T*>(y), \
+                      q, scale_f32, H)
+    if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
+#undef LLMQRT_RUN
+    if (rc) return rc;
+    return check_launch("rmsnorm");
+  }
   // gridDim.y carries the row: rows beyond 65535 are launched in panels
   const int cl = vec ? pick_cluster(M, H) : 1;
   const int64_t slice = H / cl;

@@ -159,11 +159,14 @@ class Qwen2Decoder:
             glue.rope_kv_write(q, k, v, self.cos, self.sin, pos0=self.pos, pos_dev=self.pos_dev if decode else None,
                                k_cache=kc, v_cache=vc)
             if decode:
-                attn = attention.attn_decode(q.reshape(B, self.hq, d), kc, vc, self.seqlens[batch0:batch0 + B],
-                                             self.max_seq_len if self._capturing else self.pos + 1)
+                # q is read in place from the fused projection output; the split-merge kernel also
+                # emits the per-token int8 row that the output projection consumes
+                _, aq, a_s = attention.attn_decode(q[:, 0], kc, vc, self.seqlens[batch0:batch0 + B],
+                                                   self.max_seq_len if self._capturing else self.pos + 1,
+                                                   quantize=True)
             else:
                 attn = attention.flash_attn_func(q, k, v, causal=True)
-            aq, _, a_s = ops.quantize_int8(attn.reshape(B * S, nq), per_token=True)
+                aq, _, a_s = ops.quantize_int8(attn.reshape(B * S, nq), per_token=True)
             o = self._allreduce(ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt))
             _, h, yq, ys = glue.rmsnorm(h, L_.ln2, cfg.rms_eps, residual=o, quantize=True, want_y=False)
             gu = ops.int8_linear_per_channel(yq, L_.wgu, None, ys, L_.sgu, dt)                # [M, 2 I_local]

@@ -113,6 +113,29 @@ def test_decode_config_shape_long_contexts():
     assert bits_equal(out, out2)                                            # fixed combine order: repeatable
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("lens", [[700, 1, 0, 513, 256], [40, 7, 64, 1, 33]])      # several KV splits / a single one
+def test_decode_strided_q_and_fused_quantization(dtype, lens):
+    # q read in place from a fused qkv row; the int8 row and scale must be exactly what the per-token
+    # quantizer makes of the 16-bit output
+    from llmqrt_b200.attention import attn_decode
+    from oracle import quant as oq
+    B, Hq, Hkv, d = len(lens), 28, 4, 128
+    Smax = max(lens)
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * d, generator=g).to(dtype).cuda()
+    kc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()
+    vc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()
+    seqlens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    q_view = qkv.view(B, Hq + 2 * Hkv, d)[:, :Hq]
+    assert not q_view.is_contiguous()
+    plain = attn_decode(q_view.contiguous(), kc, vc, seqlens, Smax)
+    out, out_q, scale = attn_decode(q_view, kc, vc, seqlens, Smax, quantize=True)
+    assert bits_equal(out, plain)
+    q_ref, s_ref = oq.quantize_int8(out.reshape(B, Hq * d).cpu(), per_token=True)
+    assert torch.equal(out_q.cpu(), q_ref) and torch.equal(scale.cpu(), s_ref.float().reshape(-1))
+
+
 def test_decode_equals_last_row_of_prefill():
     from llmqrt_b200.attention import attn_decode, flash_attn_func
     B, S, Hq, Hkv, d = 2, 333, 28, 4, 128
@@ -148,20 +171,25 @@ def test_rmsnorm_and_rope_match_reference_fixture(tag):
     assert bits_equal(q2, q) and bits_equal(k2, k)
 
 
+# 3584 and 8192: one block per row with the row in registers; 16384: cluster of blocks per row;
+# 1001: scalar accesses
+@pytest.mark.parametrize("H", [3584, 8192, 16384, 1001])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_rmsnorm_residual_and_fused_quant(dtype):
+def test_rmsnorm_residual_and_fused_quant(dtype, H):
     from llmqrt_b200 import glue
     from oracle import attention as oa
     from oracle import quant as oq
     g = torch.Generator().manual_seed(1)
-    x = torch.randn(5, 3584, generator=g).to(dtype)
-    r = torch.randn(5, 3584, generator=g).to(dtype)
-    w = (1 + 0.1 * torch.randn(3584, generator=g)).to(dtype)
+    x = torch.randn(5, H, generator=g).to(dtype)
+    r = torch.randn(5, H, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(dtype)
     y, h, q, s = glue.rmsnorm(x.cuda(), w.cuda(), 1e-6, residual=r.cuda(), quantize=True)
     h_ref = x + r
     assert bits_equal(h.cpu(), h_ref)
     frac, dist = ulp_mismatch_fraction(y.cpu(), oa.rmsnorm(h_ref, w, 1e-6))
-    assert dist <= 1 and frac < 0.02
+    # a 1-ulp (fp32) difference of the row's 1/rms moves a few elements across a rounding boundary
+    # of x*inv; the product with a weight above 1 can then land 2 ulp away
+    assert dist <= 2 and frac < 0.02
     q_ref, s_ref = oq.quantize_int8(y.cpu(), per_token=True)              # quantizer applied to the kernel's own y
     assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.float().reshape(-1))
 

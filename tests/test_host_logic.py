@@ -19,7 +19,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in include/llmqrt_b200.h but not exported"
     assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
-    assert _lib._lib.llmqrt_abi_version() == 1
+    assert _lib._lib.llmqrt_abi_version() == _lib.ABI_VERSION
     assert _lib.WORKSPACE_BYTES > 64 * 1024
 
 
