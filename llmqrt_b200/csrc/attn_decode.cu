@@ -53,8 +53,10 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
                    int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
   constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
+  LLMQRT_TIMELINE_MARK(40);
   pdl_wait();
   pdl_trigger();
+  LLMQRT_TIMELINE_MARK(41);
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int rep = Hq / Hkv;
   const int L = seqlens[b];
@@ -271,7 +273,9 @@ attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __rest
                            int8_t* __restrict__ out_q, float* __restrict__ out_scale) {
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   __shared__ float red[32];
+  LLMQRT_TIMELINE_MARK(50);
   pdl_trigger_then_wait();
+  LLMQRT_TIMELINE_MARK(51);
   const int b = blockIdx.x;
   const int L = seqlens[b];
   const int n_splits = (L + chunk - 1) / chunk;
@@ -445,3 +449,5 @@ int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cach
 }
 
 }  // extern "C"
+
+LLMQRT_TIMELINE_DUMP(attn)

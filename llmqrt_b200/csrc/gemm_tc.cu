@@ -234,14 +234,10 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
   }
 }
 
-// Optional stage timestamps of block 0 (build with -DLLMQRT_TC_TRACE): 64-bit global-timer readings
-// stored after the status word of the workspace.
-#ifdef LLMQRT_TC_TRACE
-#define TC_TRACE(slot)                                                                                  \
-  do {                                                                                                  \
-    if (blockIdx.x == 0 && prm.status)                                                                  \
-      reinterpret_cast<unsigned long long*>(prm.status + 7)[slot] = tc::global_timer_ns();             \
-  } while (0)
+// Optional stage timestamps of block 0 (build with -DLLMQRT_TIMELINE): events 52 + slot of the
+// in-situ timeline, recorded by whichever thread reaches the stage.
+#ifdef LLMQRT_TIMELINE
+#define TC_TRACE(slot) ::llmqrt::timeline_mark_block0(52u + (slot))
 #else
 #define TC_TRACE(slot) do {} while (0)
 #endif
@@ -272,9 +268,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort = &abort_flag;
+  const uint32_t abort_u32 = tc::smem_u32(&abort_flag);
   const int S = prm.splits;
   const int my_split = S > 1 ? (int)cluster_ctarank() : 0;
 
+  LLMQRT_TIMELINE_MARK(1);
   if (threadIdx.x == 0) {
     TC_TRACE(0);
     abort_flag = 0;
@@ -352,6 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           // ring already keeps more bytes in flight than HBM needs, and the activation loads then
           // queue behind the prefetches.)
           pdl_wait();
+          LLMQRT_TIMELINE_MARK(2);
           pdl_trigger();
         }
       }
@@ -370,10 +369,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           int s_w = stage_i;
           uint32_t ph_w = phase;
           for (int g = 0; g < nb; ++g) {               // wait until all slots of the burst are free
-            if (!tc::mbar_wait(tc::smem_u32(&bar_empty[s_w]), ph_w ^ 1u, abort)) { ok = false; break; }
+            tc::mbar_wait_or_flag(tc::smem_u32(&bar_empty[s_w]), ph_w ^ 1u, abort_u32);
             if (++s_w == kStages) { s_w = 0; ph_w ^= 1u; }
           }
-          if (!ok) break;
+          if (*abort) { ok = false; break; }           // a wait ran out (here or in another role)
           for (int g = 0; g < nb; ++g) {
             int kr = it0 + g + rot;
             if (kr >= kb_count) kr -= kb_count;
@@ -415,9 +414,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int it = 0; it < kb_count; ++it) {
-          if (!tc::mbar_wait(tc::smem_u32(&bar_full[stage_i]), phase, abort)) { ok = false; break; }
+          // No result and no tcgen05 fence here: the tiles were written by TMA, whose completion on
+          // the barrier orders them before MMAs issued after the wait; the flag is checked per tile.
+          tc::mbar_wait_or_flag(tc::smem_u32(&bar_full[stage_i]), phase, abort_u32);
           if (it == 0) TC_TRACE(2);
-          tc::fence_after_sync();
           const uint32_t sp = tc::smem_u32(tiles + stage_i * kStageBytes);
           const uint64_t dp = tc::smem_desc_k_major_sw128(sp);
           const uint64_t dq = tc::smem_desc_k_major_sw128(sp + kBM * kRowBytes);
@@ -430,7 +430,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           tc::mma_commit(tc::smem_u32(&bar_empty[stage_i]));    // frees the stage once the MMAs retire
           if (++stage_i == kStages) { stage_i = 0; phase ^= 1u; }
         }
-        if (!ok) break;
+        if (*abort) { ok = false; break; }
         tc::mma_commit(tc::smem_u32(&bar_acc_full[buf]));        // accumulator complete
         TC_TRACE(3);
         acc_phase[buf] ^= 1u;
@@ -573,6 +573,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   tc::fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) TC_TRACE(6);
+  LLMQRT_TIMELINE_MARK(3);
   if (warp == 1) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
@@ -745,3 +746,5 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
 }
 
 }  // namespace llmqrt
+
+LLMQRT_TIMELINE_DUMP(gemm)

@@ -160,7 +160,9 @@ silu_mul_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, in
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_amax;
+  LLMQRT_TIMELINE_MARK(20);
   pdl_trigger_then_wait();
+  LLMQRT_TIMELINE_MARK(21);
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -217,7 +219,9 @@ __global__ void __launch_bounds__(1024)
 rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ x_out,
                     const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
                     float* __restrict__ scale_f32, int64_t H) {
+  LLMQRT_TIMELINE_MARK(10);
   pdl_trigger_then_wait();
+  LLMQRT_TIMELINE_MARK(11);
   const int64_t m = blockIdx.x, u = threadIdx.x;
   const bool on = u * 8 < H;
   const int64_t off = m * H;
@@ -291,8 +295,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ q, int64_t q_token_stride, 
                                      T* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
                                      int pos0, const int32_t* __restrict__ pos_dev, const float* __restrict__ cos_tab,
                                      const float* __restrict__ sin_tab, int table_rows, int S, int Hq, int Hkv, int d) {
+  LLMQRT_TIMELINE_MARK(30);
   pdl_wait();
   pdl_trigger();
+  LLMQRT_TIMELINE_MARK(31);
   const int token = blockIdx.x, head = blockIdx.y;
   const int b = token / S, s = token - b * S;
   const int pos = (pos_dev ? *pos_dev : pos0) + s;
@@ -434,3 +440,5 @@ int llmqrt_rope_kv_write(void* q, int64_t q_token_stride, void* k, const void* v
 }
 
 }  // extern "C"
+
+LLMQRT_TIMELINE_DUMP(glue)

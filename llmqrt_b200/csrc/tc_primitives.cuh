@@ -42,14 +42,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // raised `*abort`.  On a time-out it raises `*abort` itself.  Returns true when the phase completed.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
-  // Fast path: no clock is read until the barrier has failed to complete for a while (the global
-  // timer is slow to read and this loop sits on the critical path of every pipeline stage).
-  for (int it = 0; it < 2048; ++it)
-    if (mbar_try_wait(bar, parity)) return true;
+  // One probe first: a counted retry loop gets unrolled into a chain of predicated probes, and a
+  // barrier that is already complete then pays the latency of every one of them.
+  if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 0u) {
+    if ((it & 63u) == 0u) {
       if (*abort) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) {
         *abort = 1;
@@ -57,6 +57,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+
+// The same bounded wait for the per-stage waits of the pipeline, where the single thread that issues
+// the copies or the MMAs pays for every dependent instruction: no result is returned (a conditional
+// exit from the issuing loop costs more than the probe itself).  On a time-out, or when another
+// thread has raised the flag, the 32-bit flag at shared address `abort_smem` is set / left set and
+// the caller, which checks the flag once per tile or burst, carries on until then with whatever the
+// stage holds.
+__device__ __forceinline__ void mbar_wait_or_flag(uint32_t bar, uint32_t parity, uint32_t abort_smem) {
+  asm volatile(
+      "{\n\t.reg .pred P1, P2;\n\t.reg .u32 c;\n\t.reg .u64 t0, t1;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%0], %1;\n\t"
+      "@P1 bra W_DONE;\n\t"
+      "mov.u64 t0, %%globaltimer;\n\t"
+      "W_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%0], %1;\n\t"
+      "@P1 bra W_DONE;\n\t"
+      "ld.volatile.shared.u32 c, [%2];\n\t"
+      "setp.ne.u32 P2, c, 0;\n\t"
+      "@P2 bra W_DONE;\n\t"
+      "mov.u64 t1, %%globaltimer;\n\t"
+      "sub.u64 t1, t1, t0;\n\t"
+      "setp.lt.u64 P2, t1, %3;\n\t"
+      "@P2 bra W_LOOP;\n\t"
+      "mov.u32 c, 1;\n\t"
+      "st.volatile.shared.u32 [%2], c;\n\t"
+      "W_DONE:\n\t}"
+      ::"r"(bar), "r"(parity), "r"(abort_smem), "l"(kWaitLimitNs)
+      : "memory");
 }
 
 // Named barrier over `nthreads` threads that also ORs a predicate across them (uniform result).
