@@ -45,6 +45,79 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b)
   }
 }
 
+// Merges the split partials of sequence b (all heads) into `out` and, with out_q, quantizes the merged
+// token row to int8 with a per-token scale -- the arithmetic of the stand-alone per-token quantizer
+// applied to the 16-bit result.  Called by every thread of a block; `row_s` (shared, Hq * D 16-bit
+// words, needed only with out_q) and `red` (shared, 32 floats) are scratch.
+template <bool BF16, int D>
+__device__ __forceinline__ void merge_sequence(int b, int n_splits, uint16_t* __restrict__ out, int Hq, int max_splits,
+                                               const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                               int8_t* __restrict__ out_q, float* __restrict__ out_scale,
+                                               uint16_t* row_s, float* red) {
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  const int units = Hq * D / 8;
+  uint16_t* orow = out + (int64_t)b * Hq * D;
+  float amax = 0.f;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    __align__(16) T e[8];
+    if (n_splits <= 1) {
+      *reinterpret_cast<uint4*>(e) = __ldcg(reinterpret_cast<const uint4*>(orow + u * 8));
+    } else {
+      const int hq = (u * 8) / D, dd = (u * 8) % D;
+      const int64_t base = ((int64_t)b * Hq + hq) * max_splits;
+      // one pass with a running maximum (splits in index order): the loads of successive splits do
+      // not depend on one another, so several are in flight at a time
+      float M = -INFINITY, lsum = 0.f, osum[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) osum[j] = 0.f;
+#pragma unroll 4
+      for (int s = 0; s < n_splits; ++s) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2));
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * D + dd));
+        const float4 c = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * D + dd + 4));
+        const float Mn = fmaxf(M, ml.x);
+        const float keep = M > -INFINITY ? exp2f(M - Mn) : 0.f;
+        const float f = ml.x > -INFINITY ? exp2f(ml.x - Mn) : 0.f;
+        M = Mn;
+        lsum = lsum * keep + ml.y * f;
+        osum[0] = osum[0] * keep + a.x * f; osum[1] = osum[1] * keep + a.y * f;
+        osum[2] = osum[2] * keep + a.z * f; osum[3] = osum[3] * keep + a.w * f;
+        osum[4] = osum[4] * keep + c.x * f; osum[5] = osum[5] * keep + c.y * f;
+        osum[6] = osum[6] * keep + c.z * f; osum[7] = osum[7] * keep + c.w * f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(lsum > 0.f ? osum[j] / lsum : 0.f);
+      *reinterpret_cast<uint4*>(orow + u * 8) = *reinterpret_cast<const uint4*>(e);
+    }
+    if (out_q) {
+      *reinterpret_cast<uint4*>(row_s + u * 8) = *reinterpret_cast<const uint4*>(e);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(to_f32<T>(e[j])));
+    }
+  }
+  if (!out_q) return;
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+  float s = round_to<T>(fmaxf(amax, 1e-5f));
+  s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
+  if (threadIdx.x == 0) out_scale[b] = s;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    __align__(16) T e[8];
+    *reinterpret_cast<uint4*>(e) = *reinterpret_cast<const uint4*>(row_s + u * 8);
+    __align__(8) int8_t o8[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = rintf(round_to<T>(__fdiv_rn(to_f32<T>(e[j]), s)));
+      v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
+      o8[j] = (int8_t)(int)v;
+    }
+    *reinterpret_cast<uint2*>(out_q + (int64_t)b * Hq * D + u * 8) = *reinterpret_cast<const uint2*>(o8);
+  }
+}
+
 template <bool BF16, int D>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const uint16_t* __restrict__ k_cache,
@@ -262,16 +335,16 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
   }
 }
 
-// Merges the split partials of one sequence (all heads) and, optionally, quantizes the merged token
-// row to int8 with a per-token scale -- the arithmetic of the stand-alone per-token quantizer applied
-// to the 16-bit result.  One block per sequence, eight consecutive elements of a head per thread.
-// With out_q the whole row must sit in one pass of the block (Hq * D / 8 <= blockDim.x).
+// Merge of the splits, one block per sequence.  Dynamic shared memory: Hq * D 16-bit words when out_q
+// is given.  (Letting the last block of a sequence do this inside the main kernel, counted off with
+// an atomic per block, was measured slower: the round trip of the atomic holds every block's shared
+// memory for about a microsecond and the last merges form a serial tail.)
 template <bool BF16, int D>
 __global__ void __launch_bounds__(1024)
 attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int chunk,
                            int max_splits, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                            int8_t* __restrict__ out_q, float* __restrict__ out_scale) {
-  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  extern __shared__ __align__(16) uint8_t row_raw[];
   __shared__ float red[32];
   LLMQRT_TIMELINE_MARK(50);
   pdl_trigger_then_wait();
@@ -280,61 +353,8 @@ attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __rest
   const int L = seqlens[b];
   const int n_splits = (L + chunk - 1) / chunk;
   if (n_splits <= 1 && !out_q) return;             // the main kernel already wrote the result
-  const int units = Hq * D / 8;
-  uint16_t* orow = out + (int64_t)b * Hq * D;
-  float amax = 0.f;
-  float val[8];
-  for (int u = threadIdx.x; u < units; u += blockDim.x) {
-    __align__(16) T e[8];
-    if (n_splits <= 1) {
-      *reinterpret_cast<uint4*>(e) = *reinterpret_cast<const uint4*>(orow + u * 8);
-    } else {
-      const int hq = (u * 8) / D, dd = (u * 8) % D;
-      const int64_t base = ((int64_t)b * Hq + hq) * max_splits;
-      float M = -INFINITY;
-      for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-      float lsum = 0.f, osum[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) osum[j] = 0.f;
-      for (int s = 0; s < n_splits; ++s) {
-        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
-        const float f = exp2f(ml.x - M);
-        lsum += ml.y * f;
-        const float4 a = *reinterpret_cast<const float4*>(part_o + (base + s) * D + dd);
-        const float4 c = *reinterpret_cast<const float4*>(part_o + (base + s) * D + dd + 4);
-        osum[0] += a.x * f; osum[1] += a.y * f; osum[2] += a.z * f; osum[3] += a.w * f;
-        osum[4] += c.x * f; osum[5] += c.y * f; osum[6] += c.z * f; osum[7] += c.w * f;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(lsum > 0.f ? osum[j] / lsum : 0.f);
-      *reinterpret_cast<uint4*>(orow + u * 8) = *reinterpret_cast<const uint4*>(e);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      val[j] = to_f32<T>(e[j]);
-      amax = fmaxf(amax, fabsf(val[j]));
-    }
-  }
-  if (!out_q) return;
-  amax = warp_max(amax);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-  __syncthreads();
-  amax = 0.f;
-  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
-  float s = round_to<T>(fmaxf(amax, 1e-5f));
-  s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
-  if (threadIdx.x == 0) out_scale[b] = s;
-  const int u = threadIdx.x;
-  if (u < units) {
-    __align__(8) int8_t o8[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float v = rintf(round_to<T>(__fdiv_rn(val[j], s)));
-      v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
-      o8[j] = (int8_t)(int)v;
-    }
-    *reinterpret_cast<uint2*>(out_q + (int64_t)b * Hq * D + u * 8) = *reinterpret_cast<const uint2*>(o8);
-  }
+  merge_sequence<BF16, D>(b, n_splits, out, Hq, max_splits, part_o, part_ml, out_q, out_scale,
+                          reinterpret_cast<uint16_t*>(row_raw), red);
 }
 
 __global__ void kv_append_kernel(uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, int64_t batch_stride16,
@@ -376,16 +396,18 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   static_assert(smem >= kWarps * 8 * D * 4, "ring too small for the merge tile");
   auto kern = attn_decode_kernel<BF16, D>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
+  const bool need_merge = max_splits > 1 || out_q != nullptr;
   if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
                               reinterpret_cast<const uint16_t*>(q), qbs, reinterpret_cast<const uint16_t*>(kc),
                               reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
                               Hq, Hkv, chunk, max_splits, scale, softcap, part_o, part_ml))
     return rc;
   if (int rc = check_launch("attn_decode")) return rc;
-  if (max_splits > 1 || out_q) {
+  if (need_merge) {
     const int units = Hq * D / 8;
     const int threads = units >= 1024 ? 1024 : (units + 31) / 32 * 32;
-    if (int rc = launch_chained(attn_decode_combine_kernel<BF16, D>, dim3(B), dim3(threads), 0, st, 1, seqlens,
+    const size_t row_smem = out_q ? (size_t)Hq * D * 2 : 0;
+    if (int rc = launch_chained(attn_decode_combine_kernel<BF16, D>, dim3(B), dim3(threads), row_smem, st, 1, seqlens,
                                 reinterpret_cast<uint16_t*>(out), Hq, chunk, max_splits,
                                 static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out_q,
                                 out_scale))

@@ -66,8 +66,8 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // predecessor.  Safe because every chained kernel waits before it reads or writes anything else, and
 // a wait only returns after the predecessor, hence the predecessor's predecessor, has completed.
 __device__ __forceinline__ void pdl_trigger_then_wait() {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
 }
 bool pdl_enabled();   // capi.cu: on unless the environment variable LLMQRT_PDL is "0"
 
@@ -90,12 +90,20 @@ __device__ __forceinline__ void timeline_mark(unsigned id) {
     if (i < kTimelineCap) g_timeline.ev[i] = (t & ~0x3full) | (id & 0x3fu);
   }
 }
-__device__ __forceinline__ void timeline_mark_block0(unsigned id) {      // any single thread of block 0
-  if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const unsigned i = atomicAdd(&g_timeline.n, 1u);
-    if (i < kTimelineCap) g_timeline.ev[i] = (t & ~0x3full) | (id & 0x3fu);
+// Appends marks taken as SM-clock readings (clock64(), 0 = not taken): they are placed on the global
+// timer axis relative to "now", assuming 1.9 SM cycles per ns.  One thread, once per block.
+__device__ __forceinline__ void timeline_flush(const long long* clk, const unsigned* ids, int n) {
+  unsigned long long g1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+  const long long c1 = clock64();
+  int valid = 0;
+  for (int i = 0; i < n; ++i) valid += clk[i] != 0;
+  unsigned at = atomicAdd(&g_timeline.n, (unsigned)valid);
+  for (int i = 0; i < n; ++i) {
+    if (clk[i] == 0) continue;
+    const unsigned long long t = g1 - (unsigned long long)((c1 - clk[i]) * 10 / 19);
+    if (at < kTimelineCap) g_timeline.ev[at] = (t & ~0x3full) | (ids[i] & 0x3fu);
+    ++at;
   }
 }
 #define LLMQRT_TIMELINE_MARK(id) ::llmqrt::timeline_mark(id)

@@ -57,7 +57,11 @@ struct TcParams {
 
 template <int BN> constexpr int stage_bytes() { return (kBM + BN) * kRowBytes; }
 template <int BN> constexpr int num_stages() {
-  int s = (kSmemBudget - 1024 - kEpiStageBytes) / stage_bytes<BN>();
+  // The decode-sized tiles (BN <= 128) leave about 28 KiB of the SM's shared memory unclaimed, so that
+  // blocks of the small kernel that precedes the GEMM in a chain can share the SM with a GEMM block
+  // that has been launched early and is streaming its first weights.
+  constexpr int budget = BN > 128 ? kSmemBudget : 200 * 1024;
+  int s = (budget - 1024 - kEpiStageBytes) / stage_bytes<BN>();
   return s > 8 ? 8 : s;
 }
 template <int BN> constexpr int smem_bytes() { return num_stages<BN>() * stage_bytes<BN>() + kEpiStageBytes + 1024; }
@@ -98,6 +102,12 @@ __device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_local, uint32_t sr
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "r"(src_local), "r"(bytes), "r"(bar)
                : "memory");
+}
+// One arrival on the mbarrier at the same shared-memory offset in CTA `cta_rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_local, uint32_t cta_rank) {
+  uint32_t bar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local), "r"(cta_rank));
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -237,9 +247,19 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
 // Optional stage timestamps of block 0 (build with -DLLMQRT_TIMELINE): events 52 + slot of the
 // in-situ timeline, recorded by whichever thread reaches the stage.
 #ifdef LLMQRT_TIMELINE
-#define TC_TRACE(slot) ::llmqrt::timeline_mark_block0(52u + (slot))
+// Marks are SM-clock readings parked in shared memory (a few cycles each); thread 0 converts them to
+// global-timer time and appends them to the timeline when the block tears down.
+#define TC_TRACE(slot)                                                         \
+  do {                                                                         \
+    if (blockIdx.x == 0) tr_clk[slot] = clock64();                             \
+  } while (0)
 #else
 #define TC_TRACE(slot) do {} while (0)
+#endif
+
+#ifdef LLMQRT_TIMELINE
+__device__ unsigned long long g_last_done;   // latest exit time over the blocks of the launch in flight
+__device__ unsigned long long g_cta_times[4][512];   // per block of the latest N == K == 3584 launch: enter, dependency met, accumulator done, exit
 #endif
 
 template <int KIND, int BN>
@@ -261,6 +281,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ __align__(8) uint64_t bar_reduce;         // split mode: counts the bytes of the incoming slices
+  __shared__ __align__(8) uint64_t bar_release;        // split mode: one arrival per peer that has received its slice
   __shared__ __align__(16) float q_scale[BN];
   __shared__ __align__(16) float q_bias[BN];
   __shared__ uint32_t tmem_base_slot;
@@ -272,8 +293,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   const int S = prm.splits;
   const int my_split = S > 1 ? (int)cluster_ctarank() : 0;
 
-  LLMQRT_TIMELINE_MARK(1);
+#ifdef LLMQRT_TIMELINE
+  __shared__ long long tr_clk[16];     // slots 0-10: stages below; 11 enter, 12 dependency met, 13 done
+  __shared__ unsigned long long tr_prev_last_done;   // when the last block of the previous launch of this kernel left
+#endif
   if (threadIdx.x == 0) {
+#ifdef LLMQRT_TIMELINE
+    for (int i = 0; i < 16; ++i) tr_clk[i] = 0;
+    if (blockIdx.x == 0) tr_prev_last_done = atomicExch(&g_last_done, 0ull);
+    if (prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[0][blockIdx.x] = tc::global_timer_ns();
+#endif
+    TC_TRACE(11);
     TC_TRACE(0);
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -285,6 +315,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       tc::mbar_init(tc::smem_u32(&bar_acc_empty[b]), 128);
     }
     tc::mbar_init(tc::smem_u32(&bar_reduce), 1);
+    tc::mbar_init(tc::smem_u32(&bar_release), (uint32_t)S);
     tc::mbar_fence_init();
     tc::tma_prefetch_descriptor(&tm_p);
     tc::tma_prefetch_descriptor(&tm_q);
@@ -314,6 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   // K range of this CTA (balanced, never empty because k_blocks >= 2 * S)
   const int kb_begin = (int)((int64_t)my_split * prm.k_blocks / S);
   const int kb_count = (int)((int64_t)(my_split + 1) * prm.k_blocks / S) - kb_begin;
+  EpiConsts ec_split = {};           // split mode: set by the epilogue warps before they wait for the MMAs
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -350,7 +382,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           // ring already keeps more bytes in flight than HBM needs, and the activation loads then
           // queue behind the prefetches.)
           pdl_wait();
-          LLMQRT_TIMELINE_MARK(2);
+          TC_TRACE(12);
+#ifdef LLMQRT_TIMELINE
+          if (prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[1][blockIdx.x] = tc::global_timer_ns();
+#endif
           pdl_trigger();
         }
       }
@@ -433,6 +468,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         if (*abort) { ok = false; break; }
         tc::mma_commit(tc::smem_u32(&bar_acc_full[buf]));        // accumulator complete
         TC_TRACE(3);
+#ifdef LLMQRT_TIMELINE
+        if (prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[2][blockIdx.x] = tc::global_timer_ns();
+#endif
         acc_phase[buf] ^= 1u;
         buf ^= 1;
       }
@@ -451,6 +489,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       if (S == 1) {
         epi_barrier();                                 // previous tile no longer reads q_scale / q_bias
         ec = epi_setup(prm, alpha, tp * kBM + et, tq * BN, BN, et, q_scale, q_bias);
+      } else {
+        // split mode: the scales of the columns this CTA owns, fetched while the MMAs still run
+        const int cpo = BN / S;
+        ec_split = epi_setup(prm, alpha, tp * kBM + et, tq * BN + my_split * cpo, cpo, et, q_scale, q_bias);
       }
       // The four epilogue warps must agree on leaving the loop: OR the failure over all 128 threads.
       const bool failed = !tc::mbar_wait(tc::smem_u32(&bar_acc_full[buf]), acc_phase[buf], abort);
@@ -498,11 +540,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     const bool healthy = abort_flag == 0;              // own MMAs finished (epilogue warps waited for them)
     const int quad = warp & 3, et = quad * 32 + lane;
     const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
-    EpiConsts ec;
+    const EpiConsts& ec = ec_split;                    // q_scale / q_bias cover only the columns this CTA owns
     if (warp >= 2 && healthy) {
-      const float alpha = prm.epi.alpha_dev ? *prm.epi.alpha_dev : prm.epi.alpha;
-      // q_scale / q_bias cover only the columns this CTA owns
-      ec = epi_setup(prm, alpha, tp * kBM + et, tq * BN + my_split * cpo, cpo, et, q_scale, q_bias);
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 8) {
@@ -526,6 +565,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
                          (uint32_t)o);
     }
     if (threadIdx.x == 64) TC_TRACE(8);
+    // Once every slice addressed to this CTA has landed, the peers' `send` buffers are no longer
+    // being read on its behalf: tell each of them.  A CTA leaves once all S owners have said so, which
+    // by then happened during its own epilogue -- no cluster barrier at the end.  Done by the otherwise
+    // idle producer thread, which waits for the slices on its own: the remote arrivals take a few
+    // hundred ns each and would hold up the epilogue warps.
+    if (threadIdx.x == 0 && healthy && tc::mbar_wait(tc::smem_u32(&bar_reduce), 0u, abort)) {
+      for (int o = 0; o < S; ++o) mbar_arrive_remote(tc::smem_u32(&bar_release), (uint32_t)o);
+    }
     bool reduce_ok = false;
     if (warp >= 2) {
       const bool failed = !healthy || !tc::mbar_wait(tc::smem_u32(&bar_reduce), 0u, abort);
@@ -560,11 +607,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         epi_drain_chunk(prm, stage, ncols, tp * kBM, j0, et);
       }
     }
-    // Nobody leaves while a peer may still be copying out of its `send` buffer: an owner passes this
-    // barrier only after all the slices addressed to it have landed.
+    // Nobody leaves while a peer may still be copying out of its `send` buffer (bounded: a peer that
+    // failed never reports, and the block then gives up with the abort flag raised).
     if (threadIdx.x == 64) TC_TRACE(10);
-    __syncwarp();
-    cluster_sync_all();
+    if (threadIdx.x == 64 && healthy) tc::mbar_wait(tc::smem_u32(&bar_release), 0u, abort);
   }
   }
 
@@ -573,7 +619,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   tc::fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) TC_TRACE(6);
-  LLMQRT_TIMELINE_MARK(3);
+#ifdef LLMQRT_TIMELINE
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    tr_clk[13] = clock64();
+    const unsigned ids[16] = {52, 53, 54, 55, 56, 57, 58, 59, 60, 61, 62, 1, 2, 3, 0, 0};
+    timeline_flush(tr_clk, ids, 14);
+    if (tr_prev_last_done) {
+      const unsigned at = atomicAdd(&g_timeline.n, 1u);
+      if (at < kTimelineCap) g_timeline.ev[at] = (tr_prev_last_done & ~0x3full) | 4u;
+    }
+  }
+  if (threadIdx.x == 0) atomicMax(&g_last_done, tc::global_timer_ns());
+  if (threadIdx.x == 0 && prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[3][blockIdx.x] = tc::global_timer_ns();
+#endif
   if (warp == 1) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
@@ -748,3 +806,8 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
 }  // namespace llmqrt
 
 LLMQRT_TIMELINE_DUMP(gemm)
+#ifdef LLMQRT_TIMELINE
+extern "C" int llmqrt_timeline_gemm_blocks(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, llmqrt::g_cta_times, sizeof(unsigned long long) * 4 * 512) == cudaSuccess ? 0 : -1;
+}
+#endif

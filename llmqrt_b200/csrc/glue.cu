@@ -212,6 +212,58 @@ __device__ __forceinline__ float block_reduce_any(float v) {
   return result;
 }
 
+// SiLU(gate) * up with the row split over the CTAs of a cluster and eight elements per thread held
+// in registers from the load to the quantized store; the row absmax is reduced in the block and then
+// across the cluster through distributed shared memory.  grid = (cluster_size, M), blockDim.x * 8 >=
+// slice.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+silu_mul_regs_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, int8_t* __restrict__ q,
+                     float* __restrict__ scale_f32, int64_t I, int64_t slice) {
+  __shared__ float slot_amax;
+  LLMQRT_TIMELINE_MARK(20);
+  pdl_trigger_then_wait();
+  LLMQRT_TIMELINE_MARK(21);
+  const int cl = gridDim.x, rank = blockIdx.x;
+  const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice, u = threadIdx.x;
+  const bool on = u * 8 < slice;
+  T h[8];
+  float f[8];
+  float amax = 0.f;
+  if (on) {
+    T g[8], up[8];
+    const T* gr = gate_up + m * ld + c0;
+    load_unit<T, true>(gr, u, g);
+    load_unit<T, true>(gr + I, u, up);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gv = to_f32<T>(g[j]);
+      const float act = round_to<T>(gv / (1.0f + expf(-gv)));             // silu in T
+      f[j] = round_to<T>(act * to_f32<T>(up[j]));                         // * up, in T
+      h[j] = from_f32<T>(f[j]);
+      amax = fmaxf(amax, fabsf(f[j]));
+    }
+    if (y) store_unit<T, true>(y + m * I + c0, u, h);
+  }
+  if (q) {
+    amax = cluster_reduce<true>(block_reduce_any<true>(amax), &slot_amax, cl);
+    float s = round_to<T>(fmaxf(amax, 1e-5f));
+    s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
+    if (rank == 0 && threadIdx.x == 0) scale_f32[m] = s;
+    if (on) {
+      __align__(8) int8_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = rintf(round_to<T>(__fdiv_rn(f[j], s)));
+        v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
+        o[j] = (int8_t)(int)v;
+      }
+      *reinterpret_cast<uint2*>(q + m * I + c0 + u * 8) = *reinterpret_cast<const uint2*>(o);
+    }
+    if (cl > 1) cg::this_cluster().sync();           // nobody leaves while its slot may still be read
+  }
+}
+
 // RMSNorm for rows of up to 8192 elements: one block per row, eight elements per thread held in
 // registers from the load to the quantized store (no staging, two block reductions).
 template <typename T>
@@ -394,12 +446,34 @@ int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* 
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = I % 8 == 0 && ld % 8 == 0 && aligned16(gate_up) && aligned16(y) &&
                    (reinterpret_cast<uintptr_t>(q) & 7) == 0;
-  const int cl = vec ? pick_cluster(M, I) : 1;
+  // Register-resident variant: the smallest cluster whose slices fit one block (8 elements per
+  // thread), widened while that still leaves every SM at most a few blocks and slices of >= 128 threads.
+  int rcl = 0;
+  if (vec) {
+    const int64_t units = I / 8;
+    for (int c = 1; c <= 8; c *= 2)
+      if (units % c == 0 && units / c <= 1024) { rcl = c; break; }
+    while (rcl && rcl < 8 && units % (rcl * 2) == 0 && units / (rcl * 2) >= 128 && M * rcl * 2 <= 4 * sm_count()) rcl *= 2;
+  }
+  const int cl = rcl ? rcl : (vec ? pick_cluster(M, I) : 1);
   const int64_t slice = I / cl;
   const size_t smem = q ? (size_t)slice * 2 : 0;
   for (int64_t m0 = 0; m0 < M; m0 += 65535) {
     const int64_t mc = (M - m0 < 65535) ? (M - m0) : 65535;
     int rc;
+    if (rcl) {
+      const unsigned threads = (unsigned)((slice / 8 + 31) / 32 * 32);
+#define LLMQRT_RUN_REGS(T)                                                                                         \
+  rc = launch_chained(silu_mul_regs_kernel<T>, dim3((unsigned)cl, (unsigned)mc, 1), dim3(threads, 1, 1), 0, st, cl, \
+                      reinterpret_cast<const T*>(gate_up) + m0 * ld, ld,                                            \
+                      y ? reinterpret_cast<T*>(y) + m0 * I : (T*)nullptr, q ? q + m0 * I : (int8_t*)nullptr,        \
+                      scale_f32 ? scale_f32 + m0 : (float*)nullptr, I, slice)
+      if (dtype == LLMQRT_F16) LLMQRT_RUN_REGS(__half); else LLMQRT_RUN_REGS(__nv_bfloat16);
+#undef LLMQRT_RUN_REGS
+      if (rc) return rc;
+      if (int rc2 = check_launch("silu_mul")) return rc2;
+      continue;
+    }
 #define LLMQRT_RUN(T, V)                                                                                       \
   rc = launch_row_kernel(silu_mul_kernel<T, V>, cl, mc, smem, st, reinterpret_cast<const T*>(gate_up) + m0 * ld, ld, \
                          y ? reinterpret_cast<T*>(y) + m0 * I : (T*)nullptr, q ? q + m0 * I : (int8_t*)nullptr,   \

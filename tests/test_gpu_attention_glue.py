@@ -136,6 +136,29 @@ def test_decode_strided_q_and_fused_quantization(dtype, lens):
     assert torch.equal(out_q.cpu(), q_ref) and torch.equal(scale.cpu(), s_ref.float().reshape(-1))
 
 
+def test_decode_quantization_single_split_without_workspace():
+    # short caches need no split partials, hence no workspace; the merge kernel still quantizes the rows
+    from llmqrt_b200 import _lib as L
+    from llmqrt_b200.attention import attn_decode
+    from oracle import quant as oq
+    B, Hq, Hkv, d, Smax = 3, 28, 4, 128, 64
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(B, Hq, d, generator=g).half().cuda()
+    kc = torch.randn(B, Smax, Hkv, d, generator=g).half().cuda()
+    vc = torch.randn(B, Smax, Hkv, d, generator=g).half().cuda()
+    seqlens = torch.tensor([64, 3, 17], dtype=torch.int32, device="cuda")
+    ref = attn_decode(q, kc, vc, seqlens, Smax)
+    out = torch.empty_like(q)
+    out_q = torch.empty(B, Hq * d, dtype=torch.int8, device="cuda")
+    scale = torch.empty(B, dtype=torch.float32, device="cuda")
+    L.call("llmqrt_attn_decode", L.ptr(q), Hq * d, L.ptr(kc), L.ptr(vc), kc.stride(0), kc.stride(1), L.ptr(seqlens),
+           L.ptr(out), L.ptr(out_q), L.ptr(scale), L.dtype_code(q.dtype), B, Hq, Hkv, d, Smax, 0.0, None,
+           L.stream(q.device))
+    assert bits_equal(out, ref)
+    q_ref, s_ref = oq.quantize_int8(out.reshape(B, Hq * d).cpu(), per_token=True)
+    assert torch.equal(out_q.cpu(), q_ref) and torch.equal(scale.cpu(), s_ref.float().reshape(-1))
+
+
 def test_decode_equals_last_row_of_prefill():
     from llmqrt_b200.attention import attn_decode, flash_attn_func
     B, S, Hq, Hkv, d = 2, 333, 28, 4, 128
@@ -195,13 +218,16 @@ def test_rmsnorm_residual_and_fused_quant(dtype, H):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_silu_mul_and_fused_quant(dtype):
+# 18944, 9472, 2368: cluster of blocks with the slice in registers; 66056: slices staged in shared
+# memory; 1001: scalar accesses
+@pytest.mark.parametrize("I", [18944, 9472, 2368, 66056, 1001])
+def test_silu_mul_and_fused_quant(dtype, I):
     from llmqrt_b200 import glue
     from oracle import quant as oq
     g = torch.Generator().manual_seed(2)
-    gu = torch.randn(6, 2 * 18944, generator=g).to(dtype)
+    gu = torch.randn(6, 2 * I, generator=g).to(dtype)
     h, q, s = glue.silu_mul(gu.cuda(), quantize=True)
-    gate, up = gu[:, :18944], gu[:, 18944:]
+    gate, up = gu[:, :I], gu[:, I:]
     ref = torch.nn.functional.silu(gate) * up
     frac, dist = ulp_mismatch_fraction(h.cpu(), ref)
     assert dist <= 1 and frac < 0.01          # expf on the GPU vs the CPU's exp
