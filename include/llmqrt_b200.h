@@ -255,6 +255,32 @@ int llmqrt_rope_kv_write(void* q, int64_t q_token_stride, void* k, const void* v
 int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M,
                     int64_t I, llmqrt_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Tensor-parallel sum of the row-parallel partial outputs (after o_proj and down_proj) over
+ * peer-mapped buffers on one NVLink/NVSwitch node, one process per GPU, up to 8 ranks.
+ * No counterpart in the reference, which has no tensor parallelism (its only multi-device mode is
+ * layer placement, runtime/core/base.py:213-221).
+ *
+ * Set-up, once per process (these calls allocate and synchronize; llmqrt_comm_allreduce does not):
+ *   llmqrt_comm_create        allocates this rank's buffer (capacity max_bytes per call) on the
+ *                             current device;
+ *   llmqrt_comm_local_handle  writes llmqrt_comm_handle_bytes() bytes identifying it; the caller
+ *                             exchanges them with the other ranks by any means (an all-gather);
+ *   llmqrt_comm_open_peer     maps rank `peer`'s buffer from its handle.
+ * llmqrt_comm_allreduce: out[i] = sum over ranks of x[i] (fp32 accumulation in rank order, one
+ * rounding; identical bits on every rank); n a multiple of 8, out may alias x.  Every rank must
+ * issue the same sequence of calls with the same n.  Waits on peers are bounded (5 s): on a
+ * time-out the output is not written and a sticky status is raised, after which further calls
+ * return without waiting; llmqrt_comm_status reads it (0 = healthy; synchronizes the device).
+ * ------------------------------------------------------------------------------------------ */
+int llmqrt_comm_create(int rank, int world, int64_t max_bytes, void** comm_out);
+int llmqrt_comm_handle_bytes(void);
+int llmqrt_comm_local_handle(void* comm, void* handle_out);
+int llmqrt_comm_open_peer(void* comm, int peer, const void* handle);
+int llmqrt_comm_allreduce(void* comm, const void* x, void* out, int dtype, int64_t n, llmqrt_stream_t stream);
+int llmqrt_comm_status(void* comm, int32_t* status_out);
+int llmqrt_comm_destroy(void* comm);
+
 #ifdef __cplusplus
 }
 #endif

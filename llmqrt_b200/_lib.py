@@ -57,6 +57,13 @@ _PROTOS = {
     "llmqrt_rope_kv_write": (c_int, [P, I64, P, P, I64, P, P, I64, I64, c_int32, P, P, P, I64, I32, I64, I64, I64,
                                      I64, I64, P]),
     "llmqrt_silu_mul": (c_int, [P, I64, P, P, P, I32, I64, I64, P]),
+    "llmqrt_comm_create": (c_int, [I32, I32, I64, ctypes.POINTER(c_void_p)]),
+    "llmqrt_comm_handle_bytes": (c_int, []),
+    "llmqrt_comm_local_handle": (c_int, [P, P]),
+    "llmqrt_comm_open_peer": (c_int, [P, I32, P]),
+    "llmqrt_comm_allreduce": (c_int, [P, P, P, I32, I64, P]),
+    "llmqrt_comm_status": (c_int, [P, ctypes.POINTER(ctypes.c_int32)]),
+    "llmqrt_comm_destroy": (c_int, [P]),
 }
 
 EXPORTS = tuple(_PROTOS)
@@ -75,7 +82,7 @@ def _bind(lib: ctypes.CDLL) -> list[str]:
     return missing
 
 
-ABI_VERSION = 2          # llmqrt_abi_version() of the sources these prototypes describe
+ABI_VERSION = 3          # llmqrt_abi_version() of the sources these prototypes describe
 
 _missing = _bind(_lib)
 if not _missing and _lib.llmqrt_abi_version() != ABI_VERSION:

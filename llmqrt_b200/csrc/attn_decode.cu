@@ -24,7 +24,7 @@ namespace {
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kRing = 3;            // cp.async stages per warp
+constexpr int kRing = 3;            // cp.async stages per warp (2 measured slower: too few bytes in flight)
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");

@@ -17,12 +17,13 @@ The lm_head is column-parallel over the vocabulary; greedy sampling reduces (max
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Optional
 
 import torch
 
 from . import attention, glue, ops
-from .tp import allreduce_sum, greedy_select, head_assignment, rows_of_heads
+from .tp import PeerAllreduce, allreduce_sum, greedy_select, head_assignment, rows_of_heads
 
 
 @dataclasses.dataclass
@@ -74,6 +75,11 @@ class Qwen2Decoder:
         self.cfg, self.device, self.tp, self.rank, self.group = cfg, torch.device(device), tp, rank, group
         self.batch, self.max_seq_len = batch, max_seq_len
         d, dt, dev = cfg.head_dim, cfg.dtype, self.device
+        # Decode-sized partial sums go over peer-mapped buffers (LLMQRT_ALLREDUCE=nccl keeps NCCL for
+        # everything); prefill-sized ones always use NCCL.
+        self.comm = None
+        if tp > 1 and os.environ.get("LLMQRT_ALLREDUCE", "peer") != "nccl":
+            self.comm = PeerAllreduce(self.device, rank, tp, max(batch, 8) * cfg.hidden * 2, group)
         self.q_heads, self.kv_heads = head_assignment(cfg.num_heads, cfg.num_kv_heads, tp, rank)
         self.hq, self.hkv = len(self.q_heads), len(self.kv_heads)
         if cfg.intermediate % tp or (cfg.intermediate // tp) % 16:
@@ -141,7 +147,7 @@ class Qwen2Decoder:
         return n + self.lm_head.numel() * self.lm_head.element_size()
 
     def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
-        return allreduce_sum(x, self.tp, self.group)
+        return allreduce_sum(x, self.tp, self.group, self.comm)
 
     def _layers_forward(self, h: torch.Tensor, B: int, S: int, decode: bool, batch0: int = 0) -> torch.Tensor:
         """h [B*S, hidden] -> hidden state before the final norm.  decode: S == 1, positions from pos_dev."""

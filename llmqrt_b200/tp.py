@@ -57,8 +57,62 @@ def greedy_select(val: torch.Tensor, idx: torch.Tensor, tp: int, group=None) -> 
     return idxs.gather(0, best)[0]
 
 
-def allreduce_sum(x: torch.Tensor, tp: int, group=None) -> torch.Tensor:
-    """In-place sum of the row-parallel partial outputs over the tensor-parallel group."""
+class PeerAllreduce:
+    """Sum all-reduce of small 16-bit tensors over buffers that every rank of `group` maps from every
+    other rank (one node, one process per GPU): llmqrt_comm_* of the C ABI.
+
+    Construction is collective (an all-gather of the buffer handles and a barrier).  `allreduce` is
+    in place, allocates nothing and can be captured in a CUDA graph; every rank must issue the same
+    sequence of calls.  `check()` reads the sticky status the kernels raise when a bounded wait on a
+    peer ran out (it synchronizes the device).
+    """
+
+    def __init__(self, device: torch.device, rank: int, world: int, max_bytes: int, group=None):
+        import ctypes
+
+        from . import _lib as L
+        self._L, self.device, self.max_bytes = L, device, int(max_bytes)
+        self._comm = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            L.call("llmqrt_comm_create", rank, world, self.max_bytes, ctypes.byref(self._comm))
+            nbytes = L._lib.llmqrt_comm_handle_bytes()
+            buf = ctypes.create_string_buffer(nbytes)
+            L.call("llmqrt_comm_local_handle", self._comm, buf)
+            mine = torch.tensor(list(buf.raw), dtype=torch.uint8, device=device)
+            handles = [torch.empty_like(mine) for _ in range(world)]
+            torch.distributed.all_gather(handles, mine, group=group)
+            for peer in range(world):
+                if peer != rank:
+                    L.call("llmqrt_comm_open_peer", self._comm, peer, bytes(handles[peer].cpu().tolist()))
+            torch.distributed.barrier(group=group)            # every buffer is mapped everywhere before first use
+
+    def eligible(self, x: torch.Tensor) -> bool:
+        return (x.is_contiguous() and x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0
+                and x.numel() * 2 <= self.max_bytes and x.data_ptr() % 16 == 0)
+
+    def allreduce(self, x: torch.Tensor) -> torch.Tensor:
+        L = self._L
+        with torch.cuda.device(self.device):
+            L.call("llmqrt_comm_allreduce", self._comm, L.ptr(x), L.ptr(x), L.dtype_code(x.dtype), x.numel(),
+                   L.stream(self.device))
+        return x
+
+    def check(self) -> None:
+        import ctypes
+        status = ctypes.c_int32(0)
+        with torch.cuda.device(self.device):
+            self._L.call("llmqrt_comm_status", self._comm, ctypes.byref(status))
+        if status.value != 0:
+            raise RuntimeError("llmqrt_b200: a tensor-parallel peer did not deliver its partial sums in time")
+
+
+def allreduce_sum(x: torch.Tensor, tp: int, group=None, comm: PeerAllreduce | None = None) -> torch.Tensor:
+    """In-place sum of the row-parallel partial outputs over the tensor-parallel group: over the
+    peer-mapped buffers of `comm` when the tensor fits them, else NCCL (the choice depends only on the
+    tensor's size, so all ranks take the same path)."""
     if tp > 1:
-        torch.distributed.all_reduce(x, group=group)
+        if comm is not None and comm.eligible(x):
+            comm.allreduce(x)
+        else:
+            torch.distributed.all_reduce(x, group=group)
     return x

@@ -19,6 +19,30 @@ def main():
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
+    ok = True
+    # ---- the peer-buffer all-reduce alone: exact fp32 rank-order sums, back-to-back calls ----
+    from llmqrt_b200.tp import PeerAllreduce
+    comm = PeerAllreduce(dev, rank, world, 1 << 20, dist.group.WORLD)
+    for dtype in (torch.float16, torch.bfloat16):
+        for n in (8, 4096, 229376, 524288):
+            xs = []
+            for rep in range(3):                                     # three calls in flight: both parities reused
+                g = torch.Generator().manual_seed(1000 * rank + n + rep)
+                xs.append(torch.randn(n, generator=g).to(dtype).to(dev))
+            wants = []
+            for x in xs:
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                acc = torch.zeros(n, dtype=torch.float32, device=dev)
+                for p in parts:
+                    acc += p.float()
+                wants.append(acc.to(dtype))
+            gots = [comm.allreduce(x.clone()) for x in xs]
+            ok &= all(torch.equal(gv, w) for gv, w in zip(gots, wants))
+    comm.check()
+    if not ok:
+        print(f"rank {rank}: peer all-reduce mismatch")
+
     from llmqrt_b200.qwen2 import Qwen2Config, Qwen2Decoder
     cfg = Qwen2Config.tiny()
     B, S, steps, max_len = 3, 21, 3, 48
@@ -38,7 +62,8 @@ def main():
         full.append(torch.cat(parts, dim=1).cpu())
     shards = [None] * world
     dist.gather_object(model.export_shard(), shards if rank == 0 else None, dst=0)
-    ok = True
+    if model.comm is not None:
+        model.comm.check()
     if rank == 0:
         from oracle.qwen2 import Qwen2Oracle
         orc = Qwen2Oracle(cfg, shards, B, max_len)
@@ -48,7 +73,7 @@ def main():
             print("rel_fro", err)
             ok &= err < 2e-2
     flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.broadcast(flag, src=0)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)             # every rank's own checks count
     dist.barrier()
     torch.cuda.synchronize(dev)
     code = 0 if int(flag.item()) == 1 else 1
