@@ -278,6 +278,13 @@ int llmqrt_comm_handle_bytes(void);
 int llmqrt_comm_local_handle(void* comm, void* handle_out);
 int llmqrt_comm_open_peer(void* comm, int peer, const void* handle);
 int llmqrt_comm_allreduce(void* comm, const void* x, void* out, int dtype, int64_t n, llmqrt_stream_t stream);
+/* llmqrt_rmsnorm with the residual arriving as tensor-parallel partial sums: residual =
+ * all-reduce(partial) exactly as llmqrt_comm_allreduce computes it (rounded to the 16-bit type), then
+ * h = x + residual, RMSNorm and the optional per-token int8 quantization, in one kernel
+ * (H a multiple of 8, H <= 8192, M * H * 2 bytes within the communicator's capacity). */
+int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x, void* x_out, const void* weight,
+                                  float eps, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H,
+                                  llmqrt_stream_t stream);
 int llmqrt_comm_status(void* comm, int32_t* status_out);
 int llmqrt_comm_destroy(void* comm);
 

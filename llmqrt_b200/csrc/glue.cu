@@ -11,6 +11,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "peer_comm.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -264,36 +265,20 @@ silu_mul_regs_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ 
   }
 }
 
-// RMSNorm for rows of up to 8192 elements: one block per row, eight elements per thread held in
-// registers from the load to the quantized store (no staging, two block reductions).
+// RMSNorm of one row held in registers, eight elements per thread (rows of up to 8192 elements, one
+// block per row): `h` are the row's values already rounded to T (x, or x + residual), `on` says
+// whether this thread owns a unit.  Two block reductions, no staging; optional quantized store.
 template <typename T>
-__global__ void __launch_bounds__(1024)
-rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ x_out,
-                    const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
-                    float* __restrict__ scale_f32, int64_t H) {
-  LLMQRT_TIMELINE_MARK(10);
-  pdl_trigger_then_wait();
-  LLMQRT_TIMELINE_MARK(11);
-  const int64_t m = blockIdx.x, u = threadIdx.x;
-  const bool on = u * 8 < H;
+__device__ __forceinline__ void rmsnorm_regs_finish(bool on, float (&f)[8], int64_t m, int64_t u, int64_t H,
+                                                    const T* __restrict__ weight, float eps, T* __restrict__ y,
+                                                    int8_t* __restrict__ q, float* __restrict__ scale_f32) {
   const int64_t off = m * H;
   T e[8], w[8];
-  float f[8];
   float ss = 0.f;
   if (on) {
-    T r[8];
-    load_unit<T, true>(x + off, u, e);
-    if (residual) load_unit<T, true>(residual + off, u, r);
     load_unit<T, true>(weight, u, w);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float v = to_f32<T>(e[j]);
-      if (residual) v = round_to<T>(v + to_f32<T>(r[j]));                 // h = x + r in T
-      e[j] = from_f32<T>(v);
-      f[j] = v;
-      ss += v * v;
-    }
-    if (x_out) store_unit<T, true>(x_out + off, u, e);
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
   }
   ss = block_reduce_any<false>(ss);
   const float inv = rsqrtf(ss / (float)H + eps);
@@ -324,6 +309,93 @@ rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* 
       *reinterpret_cast<uint2*>(q + off + u * 8) = *reinterpret_cast<const uint2*>(o);
     }
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ x_out,
+                    const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
+                    float* __restrict__ scale_f32, int64_t H) {
+  LLMQRT_TIMELINE_MARK(10);
+  pdl_trigger_then_wait();
+  LLMQRT_TIMELINE_MARK(11);
+  const int64_t m = blockIdx.x, u = threadIdx.x;
+  const bool on = u * 8 < H;
+  const int64_t off = m * H;
+  float f[8];
+  if (on) {
+    T e[8], r[8];
+    load_unit<T, true>(x + off, u, e);
+    if (residual) load_unit<T, true>(residual + off, u, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = to_f32<T>(e[j]);
+      if (residual) v = round_to<T>(v + to_f32<T>(r[j]));                 // h = x + r in T
+      e[j] = from_f32<T>(v);
+      f[j] = v;
+    }
+    if (x_out) store_unit<T, true>(x_out + off, u, e);
+  }
+  rmsnorm_regs_finish<T>(on, f, m, u, H, weight, eps, y, q, scale_f32);
+}
+
+// The same, with the residual arriving as tensor-parallel partial sums: every rank pushes its row of
+// `partial` to all ranks through the peer-mapped buffers, gathers the W copies, adds them in rank
+// order in fp32 and rounds to T -- exactly the stand-alone all-reduce -- and goes on with
+// h = x + that sum.  One kernel instead of all-reduce + RMSNorm.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __restrict__ x, T* __restrict__ x_out,
+                         const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
+                         float* __restrict__ scale_f32, int64_t H) {
+  LLMQRT_TIMELINE_MARK(10);
+  pdl_trigger_then_wait();
+  LLMQRT_TIMELINE_MARK(11);
+  __shared__ unsigned s_seq;
+  if (threadIdx.x == 0) s_seq = comm_enter(c);
+  __syncthreads();
+  const unsigned seq = s_seq;                          // 0: the status is raised, the sum is skipped
+  const int64_t m = blockIdx.x, u = threadIdx.x;
+  const bool on = u * 8 < H;
+  const int64_t off = m * H;
+  float f[8];
+  if (on) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (seq != 0u) {
+      const uint4 pv = *reinterpret_cast<const uint4*>(partial + off + u * 8);
+      const long long word = (off + u * 8) / 4;
+      comm_push(c, seq, word, make_uint2(pv.x, pv.y));
+      comm_push(c, seq, word + 1, make_uint2(pv.z, pv.w));
+      const unsigned long long t0 = comm_timer_ns();
+      bool ok = true;
+      for (int s = 0; s < c.world && ok; ++s) {
+        uint2 d0, d1;
+        ok = comm_gather(c, seq, s, word, t0, &d0) && comm_gather(c, seq, s, word + 1, t0, &d1);
+        if (ok) {
+          const T* e0 = reinterpret_cast<const T*>(&d0);
+          const T* e1 = reinterpret_cast<const T*>(&d1);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[j] += to_f32<T>(e0[j]);
+            acc[4 + j] += to_f32<T>(e1[j]);
+          }
+        }
+      }
+    }
+    T e[8];
+    load_unit<T, true>(x + off, u, e);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float r = round_to<T>(acc[j]);                                // the all-reduced value, in T
+      const float v = round_to<T>(to_f32<T>(e[j]) + r);                   // h = x + r in T
+      e[j] = from_f32<T>(v);
+      f[j] = v;
+    }
+    if (x_out) store_unit<T, true>(x_out + off, u, e);
+  }
+  rmsnorm_regs_finish<T>(on, f, m, u, H, weight, eps, y, q, scale_f32);
 }
 
 // Cluster size for a row kernel: as many CTAs per row as needed to put about two CTAs on every SM,
@@ -434,6 +506,34 @@ int llmqrt_rmsnorm(const void* x, const void* residual, void* x_out, const void*
     if (int rc2 = check_launch("rmsnorm")) return rc2;
   }
   return LLMQRT_OK;
+}
+
+int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x, void* x_out, const void* weight,
+                                  float eps, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H,
+                                  llmqrt_stream_t stream) {
+  LLMQRT_REQUIRE(comm != nullptr, "comm_allreduce_rmsnorm: null communicator");
+  Comm* c = static_cast<Comm*>(comm);
+  LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "comm_allreduce_rmsnorm: dtype must be fp16 or bf16");
+  LLMQRT_REQUIRE(M >= 0 && M <= 0x7fffffffll && H > 0 && H % 8 == 0 && H <= 8192, "comm_allreduce_rmsnorm: need H %% 8 == 0 and H <= 8192");
+  LLMQRT_REQUIRE(M * H * 4 <= c->dev.slot_bytes, "comm_allreduce_rmsnorm: M * H exceeds the communicator's capacity");
+  if (M == 0) return LLMQRT_OK;
+  LLMQRT_REQUIRE(partial && x && weight && (y || q), "comm_allreduce_rmsnorm: null pointer");
+  LLMQRT_REQUIRE(!q || scale_f32, "comm_allreduce_rmsnorm: quantized output needs scale_f32");
+  LLMQRT_REQUIRE(aligned16(partial) && aligned16(x) && aligned16(x_out) && aligned16(weight) && aligned16(y) &&
+                 (reinterpret_cast<uintptr_t>(q) & 7) == 0, "comm_allreduce_rmsnorm: pointers must be 16-byte aligned (q: 8)");
+  for (int p = 0; p < c->dev.world; ++p)
+    LLMQRT_REQUIRE(c->dev.base[p] != nullptr, "comm_allreduce_rmsnorm: peer %d has not been opened", p);
+  const unsigned threads = (unsigned)(((H / 8) + 31) / 32 * 32);
+  int rc;
+#define LLMQRT_RUN(T)                                                                                              \
+  rc = launch_chained(allreduce_rmsnorm_kernel<T>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,                  \
+                      (cudaStream_t)stream, 1, c->dev, reinterpret_cast<const T*>(partial),                          \
+                      reinterpret_cast<const T*>(x), reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), \
+                      eps, reinterpret_cast<T*>(y), q, scale_f32, H)
+  if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
+#undef LLMQRT_RUN
+  if (rc) return rc;
+  return check_launch("allreduce_rmsnorm");
 }
 
 int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M,

@@ -1,72 +1,23 @@
 // One-shot sum all-reduce of 16-bit activations over peer-mapped buffers (NVLink / NVSwitch), for the
 // row-parallel partial outputs of a tensor-parallel decode step (a few hundred KB per call, latency
-// bound: a library all-reduce costs several times the wire time at this size).
-//
-// Every rank owns one buffer, allocated once and mapped into every other rank's process through CUDA
-// IPC.  A buffer holds, per call parity p and source rank s, a slot of 16-byte words
-//     { data[0:4 bytes], seq, data[4:8 bytes], seq }
-// -- eight payload bytes (four 16-bit values), each half tagged with the sequence number of the call
-// that wrote it, so a word proves its own arrival and no fence, flag or barrier separates the data
-// from its notification.  One call, identical on every rank (same length, same grid):
-//   push   : every thread tags its words of the local vector with the call's sequence number and
-//            stores them into slot (p, me) of EVERY rank's buffer (the peers' addresses are ordinary
-//            global pointers; 16-byte volatile stores).
-//   gather : the same thread polls its OWN rank's slots (p, s) for all s until both tags of its
-//            word carry the sequence number, adds the W copies in rank order in fp32 (same order on
-//            every rank, so all ranks get identical bits), rounds once and writes the local output.
-//            The poll is bounded (5 s): on a time-out the thread raises the buffer's sticky status
-//            word and stops; later calls see the status and return at once.
-// Two parities: a rank can run at most one call ahead of a peer (it cannot finish call k+1 before
-// that peer has pushed for k+1, which the peer does after finishing call k), so call k+1 never
-// overwrites words a peer still reads for call k, and a stale word always carries an older tag.
-// The sequence number lives in the buffer and is advanced once per call by the block that draws the
-// last ticket (after every block has read it), so the kernel can be replayed from a CUDA graph.
-//
+// bound: a library all-reduce costs several times the wire time at this size), and the set-up of the
+// communicator.  Protocol and buffer layout: peer_comm.cuh.
+//   push   : every thread tags its words of the local vector and stores them into every rank's
+//            buffer (the peers' addresses are ordinary global pointers);
+//   gather : the same thread polls its own rank's slots until its word has arrived from every rank,
+//            adds the W copies in rank order in fp32 (same order on every rank, so all ranks get
+//            identical bits), rounds once and writes the local output.
 // No multicast, no TMA, no atomics on peer memory: only stores to, and polls of, plain memory.
 #include <cstring>
 #include <new>
 
-#include "common.cuh"
+#include "peer_comm.cuh"
 
 namespace llmqrt {
 namespace {
 
-constexpr int kMaxWorld = 8;
 constexpr int kArThreads = 256;
 constexpr int kMaxBlocks = 296;
-constexpr size_t kCtrlBytes = 4096;                              // {sequence, status, ticket}
-constexpr unsigned long long kPollLimitNs = 5000000000ull;       // 5 s
-
-struct CommDev {                     // passed to the kernel by value
-  unsigned char* base[kMaxWorld];    // every rank's buffer as mapped in this process; [rank] is the local one
-  int rank, world;
-  long long slot_bytes;              // capacity of one slot (tagged words: twice the payload)
-};
-
-struct Comm {
-  CommDev dev;
-  int device;
-  bool opened[kMaxWorld];
-};
-
-__device__ __forceinline__ uint4* slot_ptr(unsigned char* base, long long slot_bytes, int parity, int src) {
-  return reinterpret_cast<uint4*>(base + kCtrlBytes + ((size_t)parity * kMaxWorld + src) * (size_t)slot_bytes);
-}
-__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned long long timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 
 // x / out are viewed as 8-byte words (four 16-bit values each).
 template <typename T>
@@ -74,49 +25,20 @@ __global__ void __launch_bounds__(kArThreads)
 peer_allreduce_kernel(CommDev c, const uint2* __restrict__ x, uint2* __restrict__ out, long long nword) {
   pdl_wait();
   pdl_trigger();
-  unsigned char* me = c.base[c.rank];
-  unsigned* ctrl = reinterpret_cast<unsigned*>(me);                    // [0] sequence, [1] status, [2] ticket
-  volatile unsigned* status = ctrl + 1;
   __shared__ unsigned s_seq;
-  __shared__ int s_bad;
-  if (threadIdx.x == 0) {
-    const unsigned seq0 = *reinterpret_cast<volatile unsigned*>(ctrl) + 1u;
-    s_seq = seq0;
-    s_bad = *status != 0u;
-    __threadfence();                                                   // the read above before the ticket below
-    // Whoever draws the last ticket knows that every block has read the old sequence number.
-    if (atomicAdd(ctrl + 2, 1u) == gridDim.x - 1) {
-      ctrl[2] = 0u;
-      *reinterpret_cast<volatile unsigned*>(ctrl) = seq0;
-    }
-  }
+  if (threadIdx.x == 0) s_seq = comm_enter(c);
   __syncthreads();
-  if (s_bad) return;
   const unsigned seq = s_seq;
-  const int parity = (int)(seq & 1u);
+  if (seq == 0u) return;                                               // status raised by an earlier call
   const long long stride = (long long)gridDim.x * kArThreads;
   const long long w0 = (long long)blockIdx.x * kArThreads + threadIdx.x;
-
-  for (long long w = w0; w < nword; w += stride) {
-    const uint2 d = x[w];
-    const uint4 tagged = make_uint4(d.x, seq, d.y, seq);
-    for (int p = 0; p < c.world; ++p) st_volatile_v4(slot_ptr(c.base[p], c.slot_bytes, parity, c.rank) + w, tagged);
-  }
-
-  const unsigned long long t0 = timer_ns();
+  for (long long w = w0; w < nword; w += stride) comm_push(c, seq, w, x[w]);
+  const unsigned long long t0 = comm_timer_ns();
   for (long long w = w0; w < nword; w += stride) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < c.world; ++s) {
-      const uint4* src = slot_ptr(me, c.slot_bytes, parity, s) + w;
-      uint4 v = ld_volatile_v4(src);
-      for (unsigned it = 1; v.y != seq || v.w != seq; ++it) {
-        if ((it & 255u) == 0u && (*status != 0u || timer_ns() - t0 > kPollLimitNs)) {
-          *status = 1u;
-          return;
-        }
-        v = ld_volatile_v4(src);
-      }
-      const uint2 d = make_uint2(v.x, v.z);
+      uint2 d;
+      if (!comm_gather(c, seq, s, w, t0, &d)) return;
       const T* e = reinterpret_cast<const T*>(&d);
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[j] += to_f32<T>(e[j]);
@@ -137,15 +59,15 @@ extern "C" {
 
 int llmqrt_comm_create(int rank, int world, int64_t max_bytes, void** comm_out) {
   LLMQRT_REQUIRE(comm_out != nullptr, "comm_create: null output");
-  LLMQRT_REQUIRE(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, "comm_create: need 0 <= rank < world <= %d", kMaxWorld);
+  LLMQRT_REQUIRE(world >= 1 && world <= kCommMaxWorld && rank >= 0 && rank < world, "comm_create: need 0 <= rank < world <= %d", kCommMaxWorld);
   LLMQRT_REQUIRE(max_bytes > 0 && max_bytes <= ((int64_t)1 << 28), "comm_create: max_bytes must be in (0, 256 MiB]");
   Comm* c = new (std::nothrow) Comm();
   LLMQRT_REQUIRE(c != nullptr, "comm_create: out of host memory");
-  for (int i = 0; i < kMaxWorld; ++i) { c->dev.base[i] = nullptr; c->opened[i] = false; }
+  for (int i = 0; i < kCommMaxWorld; ++i) { c->dev.base[i] = nullptr; c->opened[i] = false; }
   c->dev.rank = rank;
   c->dev.world = world;
   c->dev.slot_bytes = 2 * ((max_bytes + 255) / 256 * 256);            // tagged words: twice the payload
-  const size_t total = kCtrlBytes + (size_t)2 * kMaxWorld * (size_t)c->dev.slot_bytes;
+  const size_t total = kCommCtrlBytes + (size_t)2 * kCommMaxWorld * (size_t)c->dev.slot_bytes;
   void* p = nullptr;
   cudaError_t e = cudaGetDevice(&c->device);
   if (e == cudaSuccess) e = cudaMalloc(&p, total);                     // set-up allocation; calls allocate nothing

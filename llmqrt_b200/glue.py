@@ -6,11 +6,14 @@ import torch
 from . import _lib as L
 
 
-def rmsnorm(x, weight, eps: float, residual=None, quantize: bool = False, want_y: bool = True):
+def rmsnorm(x, weight, eps: float, residual=None, quantize: bool = False, want_y: bool = True, comm=None):
     """y = weight * T(x32 * rsqrt(mean(x32^2) + eps)) over the last dimension.
 
     residual: if given, h = x + residual (rounded to T) is normalised instead and also returned.
     quantize: also return the per-token int8 quantization (q, scale_f32[M]) of y.
+    comm: a tp.PeerAllreduce; `residual` then holds this rank's tensor-parallel PARTIAL sums and is
+          all-reduced over the group first -- inside the same kernel when it fits the communicator,
+          else by NCCL (`residual` is then summed in place).
     Returns (y or None, h or None, q or None, scale or None).
     """
     dev = L.require_cuda(x, weight, residual)
@@ -22,9 +25,16 @@ def rmsnorm(x, weight, eps: float, residual=None, quantize: bool = False, want_y
     y = torch.empty_like(x2) if want_y else None
     q = torch.empty((M, H), dtype=torch.int8, device=dev) if quantize else None
     s = torch.empty(M, dtype=torch.float32, device=dev) if quantize else None
+    fused = comm is not None and r2 is not None and H % 8 == 0 and H <= 8192 and comm.eligible(r2)
+    if comm is not None and r2 is not None and not fused:
+        torch.distributed.all_reduce(r2, group=comm.group)
     with torch.cuda.device(dev):
-        L.call("llmqrt_rmsnorm", L.ptr(x2), L.ptr(r2), L.ptr(h), L.ptr(weight), float(eps), L.ptr(y), L.ptr(q),
-               L.ptr(s), L.dtype_code(x.dtype), M, H, L.stream(dev))
+        if fused:
+            L.call("llmqrt_comm_allreduce_rmsnorm", comm.handle, L.ptr(r2), L.ptr(x2), L.ptr(h), L.ptr(weight),
+                   float(eps), L.ptr(y), L.ptr(q), L.ptr(s), L.dtype_code(x.dtype), M, H, L.stream(dev))
+        else:
+            L.call("llmqrt_rmsnorm", L.ptr(x2), L.ptr(r2), L.ptr(h), L.ptr(weight), float(eps), L.ptr(y), L.ptr(q),
+                   L.ptr(s), L.dtype_code(x.dtype), M, H, L.stream(dev))
     shape = x.shape
     return (y.reshape(shape) if y is not None else None, h.reshape(shape) if h is not None else None, q, s)
 

@@ -155,7 +155,10 @@ class Qwen2Decoder:
         nq, nkv = self.hq * d, self.hkv * d
         pending = None                                                 # output of the previous MLP, not yet added
         for L_ in self.layers:
-            _, h_new, xq, xs = glue.rmsnorm(h, L_.ln1, cfg.rms_eps, residual=pending, quantize=True, want_y=False)
+            # with a peer communicator the partial sums of the row-parallel projections are reduced
+            # inside the RMSNorm kernel that consumes them; without one, by NCCL right after the GEMM
+            _, h_new, xq, xs = glue.rmsnorm(h, L_.ln1, cfg.rms_eps, residual=pending, quantize=True, want_y=False,
+                                            comm=self.comm)
             if h_new is not None:
                 h = h_new
             qkv = ops.int8_linear_per_channel(xq, L_.wqkv, L_.bqkv, xs, L_.sqkv, dt)          # [M, nq + 2 nkv]
@@ -173,18 +176,23 @@ class Qwen2Decoder:
             else:
                 attn = attention.flash_attn_func(q, k, v, causal=True)
                 aq, _, a_s = ops.quantize_int8(attn.reshape(B * S, nq), per_token=True)
-            o = self._allreduce(ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt))
-            _, h, yq, ys = glue.rmsnorm(h, L_.ln2, cfg.rms_eps, residual=o, quantize=True, want_y=False)
+            o = ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt)
+            if self.comm is None:
+                o = self._allreduce(o)
+            _, h, yq, ys = glue.rmsnorm(h, L_.ln2, cfg.rms_eps, residual=o, quantize=True, want_y=False,
+                                        comm=self.comm)
             gu = ops.int8_linear_per_channel(yq, L_.wgu, None, ys, L_.sgu, dt)                # [M, 2 I_local]
             _, mq, ms = glue.silu_mul(gu, quantize=True, want_y=False)
-            pending = self._allreduce(ops.int8_linear_per_channel(mq, L_.wd, None, ms, L_.sd, dt))
+            pending = ops.int8_linear_per_channel(mq, L_.wd, None, ms, L_.sd, dt)
+            if self.comm is None:
+                pending = self._allreduce(pending)
         return h, pending
 
     _capturing = False
 
     def _head(self, h: torch.Tensor, pending: torch.Tensor) -> torch.Tensor:
         """Final norm, vocabulary-parallel lm_head, greedy token per row."""
-        y, _, _, _ = glue.rmsnorm(h, self.norm_f, self.cfg.rms_eps, residual=pending)
+        y, _, _, _ = glue.rmsnorm(h, self.norm_f, self.cfg.rms_eps, residual=pending, comm=self.comm)
         logits = ops.gemm_16bit(y, self.lm_head)                                            # [M, V/tp]
         self.last_logits = logits
         val, idx = logits.max(dim=-1)

@@ -71,7 +71,7 @@ class PeerAllreduce:
         import ctypes
 
         from . import _lib as L
-        self._L, self.device, self.max_bytes = L, device, int(max_bytes)
+        self._L, self.device, self.max_bytes, self.group = L, device, int(max_bytes), group
         self._comm = ctypes.c_void_p()
         with torch.cuda.device(device):
             L.call("llmqrt_comm_create", rank, world, self.max_bytes, ctypes.byref(self._comm))
@@ -85,6 +85,11 @@ class PeerAllreduce:
                 if peer != rank:
                     L.call("llmqrt_comm_open_peer", self._comm, peer, bytes(handles[peer].cpu().tolist()))
             torch.distributed.barrier(group=group)            # every buffer is mapped everywhere before first use
+
+    @property
+    def handle(self):
+        """The opaque communicator pointer the llmqrt_comm_* entry points take."""
+        return self._comm
 
     def eligible(self, x: torch.Tensor) -> bool:
         return (x.is_contiguous() and x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0

@@ -39,6 +39,17 @@ def main():
                 wants.append(acc.to(dtype))
             gots = [comm.allreduce(x.clone()) for x in xs]
             ok &= all(torch.equal(gv, w) for gv, w in zip(gots, wants))
+    # ---- all-reduce fused into the RMSNorm that consumes it == all-reduce, then RMSNorm ----
+    from llmqrt_b200 import glue
+    for dtype in (torch.float16, torch.bfloat16):
+        for M, H in ((5, 3584), (64, 3584), (3, 256)):
+            g = torch.Generator().manual_seed(77 + M)
+            x = torch.randn(M, H, generator=g).to(dtype).to(dev)                       # same on every rank
+            w = (1 + 0.1 * torch.randn(H, generator=g)).to(dtype).to(dev)
+            part = torch.randn(M, H, generator=torch.Generator().manual_seed(500 + rank)).to(dtype).to(dev)
+            want = glue.rmsnorm(x, w, 1e-6, residual=comm.allreduce(part.clone()), quantize=True)
+            got = glue.rmsnorm(x, w, 1e-6, residual=part.clone(), quantize=True, comm=comm)
+            ok &= all(torch.equal(a, b) for a, b in zip(got, want))
     comm.check()
     if not ok:
         print(f"rank {rank}: peer all-reduce mismatch")
