@@ -365,14 +365,16 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     if (seq != 0u) {
       const uint4 pv = *reinterpret_cast<const uint4*>(partial + off + u * 8);
-      const long long word = (off + u * 8) / 4;
+      // Word placement (any bijection works, as every rank uses the same one): the two words of a
+      // thread sit 32 words apart so that each store or poll of a warp covers 512 contiguous bytes.
+      const long long word = m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31), word1 = word + 32;
       comm_push(c, seq, word, make_uint2(pv.x, pv.y));
-      comm_push(c, seq, word + 1, make_uint2(pv.z, pv.w));
+      comm_push(c, seq, word1, make_uint2(pv.z, pv.w));
       const unsigned long long t0 = comm_timer_ns();
       bool ok = true;
       for (int s = 0; s < c.world && ok; ++s) {
         uint2 d0, d1;
-        ok = comm_gather(c, seq, s, word, t0, &d0) && comm_gather(c, seq, s, word + 1, t0, &d1);
+        ok = comm_gather(c, seq, s, word, t0, &d0) && comm_gather(c, seq, s, word1, t0, &d1);
         if (ok) {
           const T* e0 = reinterpret_cast<const T*>(&d0);
           const T* e1 = reinterpret_cast<const T*>(&d1);
@@ -515,7 +517,7 @@ int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x
   Comm* c = static_cast<Comm*>(comm);
   LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "comm_allreduce_rmsnorm: dtype must be fp16 or bf16");
   LLMQRT_REQUIRE(M >= 0 && M <= 0x7fffffffll && H > 0 && H % 8 == 0 && H <= 8192, "comm_allreduce_rmsnorm: need H %% 8 == 0 and H <= 8192");
-  LLMQRT_REQUIRE(M * H * 4 <= c->dev.slot_bytes, "comm_allreduce_rmsnorm: M * H exceeds the communicator's capacity");
+  LLMQRT_REQUIRE(M * (((H / 8) + 31) / 32 * 32) * 32 <= c->dev.slot_bytes, "comm_allreduce_rmsnorm: M * H exceeds the communicator's capacity");
   if (M == 0) return LLMQRT_OK;
   LLMQRT_REQUIRE(partial && x && weight && (y || q), "comm_allreduce_rmsnorm: null pointer");
   LLMQRT_REQUIRE(!q || scale_f32, "comm_allreduce_rmsnorm: quantized output needs scale_f32");
