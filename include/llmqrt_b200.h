@@ -269,9 +269,11 @@ int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* 
  *   llmqrt_comm_open_peer     maps rank `peer`'s buffer from its handle.
  * llmqrt_comm_allreduce: out[i] = sum over ranks of x[i] (fp32 accumulation in rank order, one
  * rounding; identical bits on every rank); n a multiple of 8, out may alias x.  Every rank must
- * issue the same sequence of calls with the same n.  Waits on peers are bounded (5 s): on a
- * time-out the output is not written and a sticky status is raised, after which further calls
- * return without waiting; llmqrt_comm_status reads it (0 = healthy; synchronizes the device).
+ * issue the same sequence of calls with the same n.  Waits on peers are bounded (5 s, or what
+ * llmqrt_comm_set_poll_limit_ms set; the limit applies to calls launched, or graphs captured,
+ * afterwards): on a time-out the output is not written and a sticky status is raised, after which
+ * further calls return without waiting; llmqrt_comm_status reads it (0 = healthy; synchronizes the
+ * device).
  * ------------------------------------------------------------------------------------------ */
 int llmqrt_comm_create(int rank, int world, int64_t max_bytes, void** comm_out);
 int llmqrt_comm_handle_bytes(void);
@@ -285,6 +287,7 @@ int llmqrt_comm_allreduce(void* comm, const void* x, void* out, int dtype, int64
 int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x, void* x_out, const void* weight,
                                   float eps, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H,
                                   llmqrt_stream_t stream);
+int llmqrt_comm_set_poll_limit_ms(void* comm, int32_t ms);
 int llmqrt_comm_status(void* comm, int32_t* status_out);
 int llmqrt_comm_destroy(void* comm);
 

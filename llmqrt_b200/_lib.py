@@ -63,6 +63,7 @@ _PROTOS = {
     "llmqrt_comm_open_peer": (c_int, [P, I32, P]),
     "llmqrt_comm_allreduce": (c_int, [P, P, P, I32, I64, P]),
     "llmqrt_comm_allreduce_rmsnorm": (c_int, [P, P, P, P, P, F, P, P, P, I32, I64, I64, P]),
+    "llmqrt_comm_set_poll_limit_ms": (c_int, [P, c_int32]),
     "llmqrt_comm_status": (c_int, [P, ctypes.POINTER(ctypes.c_int32)]),
     "llmqrt_comm_destroy": (c_int, [P]),
 }

@@ -14,6 +14,7 @@
 // its warps through shared memory and writes either the final output (single split) or an
 // unnormalised partial (max, sum, O) that a small combine kernel reduces; the combine kernel can also
 // emit the per-token int8 quantization of the result, which is what an int8 output projection reads.
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -376,9 +377,19 @@ template <bool BF16, int D>
 int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, int64_t bs, int64_t rs,
                   const int32_t* seqlens, void* out, int8_t* out_q, float* out_scale, int B, int Hq, int Hkv,
                   int max_seqlen, float softcap, void* workspace, cudaStream_t st) {
-  // keys per block: 256, halved while the grid would not cover the SMs twice
-  int chunk = 256;
-  while (chunk > 64 && (int64_t)B * Hkv * ceil_div(max_seqlen, chunk) < 2 * sm_count()) chunk /= 2;
+  // Keys per block: the smallest power of two for which all blocks are resident at once (two fit an
+  // SM), i.e. as many blocks as one wave takes and no second wave -- a block costs about 3 us beyond
+  // its keys (first loads, merge of its warps), so waves of short blocks lose to one wave of long
+  // ones (batch 64 x 4 KV heads x 1100 keys: 35 us with 256-key blocks, 26 us unsplit).
+  int chunk = 64;
+  {
+    const int64_t slots = 2 * (int64_t)sm_count();
+    while (chunk < max_seqlen && (int64_t)B * Hkv * ceil_div(max_seqlen, chunk) > slots) chunk *= 2;
+  }
+  if (const char* env = getenv("LLMQRT_ATTN_CHUNK")) {                 // experiments: force the chunk
+    const int v = atoi(env);
+    if (v >= 16 && (v & (v - 1)) == 0) chunk = v;
+  }
   int max_splits = (int)ceil_div(max_seqlen > 0 ? max_seqlen : 1, chunk);
   while (max_splits > 1 && (size_t)B * Hq * max_splits * (D + 2) * 4 > LLMQRT_WS_PARTIAL_BYTES) {
     chunk *= 2;

@@ -66,6 +66,7 @@ int llmqrt_comm_create(int rank, int world, int64_t max_bytes, void** comm_out) 
   for (int i = 0; i < kCommMaxWorld; ++i) { c->dev.base[i] = nullptr; c->opened[i] = false; }
   c->dev.rank = rank;
   c->dev.world = world;
+  c->dev.poll_limit_ns = kCommPollLimitNs;
   c->dev.slot_bytes = 2 * ((max_bytes + 255) / 256 * 256);            // tagged words: twice the payload
   const size_t total = kCommCtrlBytes + (size_t)2 * kCommMaxWorld * (size_t)c->dev.slot_bytes;
   void* p = nullptr;
@@ -129,6 +130,12 @@ int llmqrt_comm_allreduce(void* comm, const void* x, void* out, int dtype, int64
                         (cudaStream_t)stream, 1, c->dev, static_cast<const uint2*>(x), static_cast<uint2*>(out), nword);
   if (rc) return rc;
   return check_launch("peer_allreduce");
+}
+
+int llmqrt_comm_set_poll_limit_ms(void* comm, int32_t ms) {
+  LLMQRT_REQUIRE(comm != nullptr && ms > 0, "comm_set_poll_limit_ms: need a communicator and a positive limit");
+  static_cast<Comm*>(comm)->dev.poll_limit_ns = (unsigned long long)ms * 1000000ull;
+  return LLMQRT_OK;
 }
 
 int llmqrt_comm_status(void* comm, int32_t* status_out) {

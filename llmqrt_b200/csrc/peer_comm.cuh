@@ -15,8 +15,8 @@
 // overwrites words a peer still reads for call k, and a stale word always carries an older tag.
 // The sequence number lives in the buffer and is advanced once per call by the block that draws the
 // last ticket (after every block has read it), so a call can be replayed from a CUDA graph.
-// Polls are bounded (5 s): on a time-out the sticky status word of the buffer is raised and later
-// calls return without waiting.
+// Polls are bounded (5 s unless the host sets another limit): on a time-out the sticky status word of
+// the buffer is raised and later calls return without waiting.
 #pragma once
 #include "common.cuh"
 
@@ -24,12 +24,13 @@ namespace llmqrt {
 
 constexpr int kCommMaxWorld = 8;
 constexpr size_t kCommCtrlBytes = 4096;                              // {sequence, status, ticket}
-constexpr unsigned long long kCommPollLimitNs = 5000000000ull;       // 5 s
+constexpr unsigned long long kCommPollLimitNs = 5000000000ull;       // default bound of a poll: 5 s
 
 struct CommDev {                         // passed to kernels by value
   unsigned char* base[kCommMaxWorld];    // every rank's buffer as mapped in this process; [rank] is the local one
   int rank, world;
   long long slot_bytes;                  // capacity of one slot (tagged words: twice the payload)
+  unsigned long long poll_limit_ns;      // bound of a poll
 };
 
 struct Comm {                            // what the opaque handle of the C ABI points to
@@ -86,7 +87,7 @@ __device__ __forceinline__ bool comm_gather(const CommDev& c, unsigned seq, int 
   const uint4* src = comm_slot(c.base[c.rank], c.slot_bytes, (int)(seq & 1u), s) + word;
   uint4 v = comm_ld_v4(src);
   for (unsigned it = 1; v.y != seq || v.w != seq; ++it) {
-    if ((it & 255u) == 0u && (*status != 0u || comm_timer_ns() - t0 > kCommPollLimitNs)) {
+    if ((it & 255u) == 0u && (*status != 0u || comm_timer_ns() - t0 > c.poll_limit_ns)) {
       *status = 1u;
       return false;
     }

@@ -1,4 +1,5 @@
-"""Host-side tensor-parallel logic (no kernels): head placement, shard slicing, sampling reduction.
+"""Host-side tensor-parallel logic: head placement, shard slicing, sampling reduction, and the handle
+of the peer-buffer all-reduce (llmqrt_comm_* of the C ABI).
 
 The reference has no tensor parallelism (its only multi-device mode is accelerate's layer placement,
 runtime/core/base.py:213-221); this is the Megatron column/row scheme added around the quantized
@@ -101,6 +102,10 @@ class PeerAllreduce:
             L.call("llmqrt_comm_allreduce", self._comm, L.ptr(x), L.ptr(x), L.dtype_code(x.dtype), x.numel(),
                    L.stream(self.device))
         return x
+
+    def set_poll_limit_ms(self, ms: int) -> None:
+        """Bound of the waits on peers for calls launched (or graphs captured) from now on."""
+        self._L.call("llmqrt_comm_set_poll_limit_ms", self._comm, int(ms))
 
     def check(self) -> None:
         import ctypes

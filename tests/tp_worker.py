@@ -54,6 +54,26 @@ def main():
     if not ok:
         print(f"rank {rank}: peer all-reduce mismatch")
 
+    # ---- a peer that does not deliver: the bounded wait runs out, the kernel returns, the status is raised ----
+    # The failure is made on the host (the last rank skips the call); nothing waits on that rank's GPU.
+    lame = PeerAllreduce(dev, rank, world, 4096, dist.group.WORLD)
+    lame.set_poll_limit_ms(200)
+    t = torch.ones(1024, dtype=torch.float16, device=dev)
+    if rank != world - 1:
+        lame.allreduce(t)
+        torch.cuda.synchronize(dev)                              # returns after ~0.2 s, context intact
+        try:
+            lame.check()
+            ok = False
+            print(f"rank {rank}: the missing peer went unnoticed")
+        except RuntimeError:
+            pass
+        lame.allreduce(t)                                        # sticky status: returns without waiting
+        torch.cuda.synchronize(dev)
+    else:
+        lame.check()                                             # the rank that skipped has seen no time-out
+    dist.barrier()
+
     from llmqrt_b200.qwen2 import Qwen2Config, Qwen2Decoder
     cfg = Qwen2Config.tiny()
     B, S, steps, max_len = 3, 21, 3, 48
