@@ -216,6 +216,25 @@ int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cach
                        int8_t* out_q, float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
                        int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream);
 
+/* llmqrt_attn_decode with the work on the newest token folded in (the newest token of sequence b is
+ * cache row seqlens[b] - 1, i.e. seqlens already counts it):
+ *   cos_table / sin_table (fp32 [table_rows, d/2], may be NULL): rotary embedding, half-split pairing,
+ *     of q -- in registers, q itself is not modified -- and of the new key, at angle row
+ *     seqlens[b] - 1 (rows outside the table: no rotation and no cache write);
+ *   k_new / v_new ([B, Hkv, d] with batch stride kv_batch_stride, may be NULL): the new key (rotated)
+ *     and value are written into the caches at that row before the row is read.
+ * One kernel instead of rotary + cache write + attention.
+ * ref: flash_attn_with_kvcache(q, k_cache, v_cache, k=, v=, rotary_cos=, rotary_sin=, cache_seqlens=,
+ *      rotary_interleaved=False) of the flash-attn package, whose append-and-attend form the reference
+ *      calls at runtime/nn_models/modules/nonlinear/attn.py:300-315 after applying
+ *      RoPE.forward (attn.py:53-87) and WindowedCache.update_kv (cache.py:41-46) itself. */
+int llmqrt_attn_decode_append(const void* q, int64_t q_batch_stride, const void* k_new, const void* v_new,
+                              int64_t kv_batch_stride, const float* cos_table, const float* sin_table,
+                              int64_t table_rows, void* k_cache, void* v_cache, int64_t cache_batch_stride,
+                              int64_t cache_row_stride, const int32_t* seqlens, void* out, int8_t* out_q,
+                              float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
+                              int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream);
+
 /* Prefill attention over the new tokens: q [B, S, Hq, d], k / v [B, S, Hkv, d], out [B, S, Hq, d],
  * token stride given in elements (heads and d contiguous), causal mask optional.
  * ref: flash_attn_func call site, runtime/nn_models/modules/nonlinear/attn.py:283-298. */

@@ -52,7 +52,9 @@ _PROTOS = {
     "llmqrt_gemm_16bit": (c_int, [P, I64, P, I64, P, P, I64, I32, I64, I64, I64, P, P]),
     "llmqrt_kv_append": (c_int, [P, P, I64, I64, P, P, P, c_int32, I32, I64, I64, I64, I64, I64, P]),
     "llmqrt_attn_decode": (c_int, [P, I64, P, P, I64, I64, P, P, P, P, I32, I64, I64, I64, I64, I64, F, P, P]),
-    "llmqrt_attn_prefill": (c_int, [P, I64, P, P, I64, P, I64, I32, I64, I64, I64, I64, I64, I32, F, P]),
+    "llmqrt_attn_decode_append": (c_int, [P, I64, P, P, I64, P, P, I64, P, P, I64, I64, P, P, P, P, I32, I64, I64,
+                                          I64, I64, I64, F, P, P]),
+    "llmqrt_attn_prefill":(c_int, [P, I64, P, P, I64, P, I64, I32, I64, I64, I64, I64, I64, I32, F, P]),
     "llmqrt_rmsnorm": (c_int, [P, P, P, P, F, P, P, P, I32, I64, I64, P]),
     "llmqrt_rope_kv_write": (c_int, [P, I64, P, P, I64, P, P, I64, I64, c_int32, P, P, P, I64, I32, I64, I64, I64,
                                      I64, I64, P]),

@@ -119,12 +119,35 @@ __device__ __forceinline__ void merge_sequence(int b, int n_splits, uint16_t* __
   }
 }
 
+// Optional work folded into the attention kernel for the newest token of every sequence (row
+// seqlens[b] - 1 of the cache): rotary embedding of q (cos_tab / sin_tab: fp32 [table_rows, D/2],
+// half-split pairing, angle row = the token's cache row) and, with k_new / v_new, rotation of the new
+// key and the write of key and value into the cache before the block that covers that row reads it.
+struct DecodeAppend {
+  const uint16_t* k_new;             // [B, Hkv, D] with batch stride kv_batch_stride, or null
+  const uint16_t* v_new;
+  long long kv_batch_stride;
+  const float* cos_tab;              // null: no rotation
+  const float* sin_tab;
+  int table_rows;
+};
+
+template <bool BF16> __device__ __forceinline__ float bits_to_f32(uint16_t h) {
+  if constexpr (BF16) return __uint_as_float((uint32_t)h << 16);
+  else return __half2float(__ushort_as_half(h));
+}
+template <bool BF16> __device__ __forceinline__ uint16_t f32_to_bits(float f) {
+  if constexpr (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+  else return __half_as_ushort(__float2half_rn(f));
+}
+
 template <bool BF16, int D>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const uint16_t* __restrict__ k_cache,
                    const uint16_t* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
                    const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int Hkv, int chunk,
-                   int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                   int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   DecodeAppend ap) {
   constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
   constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
   LLMQRT_TIMELINE_MARK(40);
@@ -151,6 +174,53 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
       if (g < rep) v = *reinterpret_cast<const uint4*>(qrow + 8 * (4 * j + t));
       qf[j][0] = v.x; qf[j][1] = v.y; qf[j][2] = v.z; qf[j][3] = v.w;
     }
+  }
+
+  // ---- newest token: rotate q in registers; the block that covers its cache row writes K and V ----
+  const int pos = L - 1;
+  const bool rotate = ap.cos_tab != nullptr && pos >= 0 && pos < ap.table_rows;
+  if (rotate) {
+    // chunk 4j+t pairs with chunk 4(j + NJ/2)+t: element i with i + D/2, both held by this thread
+    const float* cr = ap.cos_tab + (int64_t)pos * (D / 2);
+    const float* sr = ap.sin_tab + (int64_t)pos * (D / 2);
+#pragma unroll
+    for (int j = 0; j < NJ / 2; ++j) {
+      const int i0 = 8 * (4 * j + t);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float2 cs = *reinterpret_cast<const float2*>(cr + i0 + 2 * w);
+        const float2 sn = *reinterpret_cast<const float2*>(sr + i0 + 2 * w);
+        const uint32_t lo = qf[j][w], hi = qf[j + NJ / 2][w];
+        const float a0 = bits_to_f32<BF16>((uint16_t)(lo & 0xffffu)), a1 = bits_to_f32<BF16>((uint16_t)(lo >> 16));
+        const float b0 = bits_to_f32<BF16>((uint16_t)(hi & 0xffffu)), b1 = bits_to_f32<BF16>((uint16_t)(hi >> 16));
+        qf[j][w] = (uint32_t)f32_to_bits<BF16>(a0 * cs.x - b0 * sn.x) |
+                   ((uint32_t)f32_to_bits<BF16>(a1 * cs.y - b1 * sn.y) << 16);
+        qf[j + NJ / 2][w] = (uint32_t)f32_to_bits<BF16>(a0 * sn.x + b0 * cs.x) |
+                            ((uint32_t)f32_to_bits<BF16>(a1 * sn.y + b1 * cs.y) << 16);
+      }
+    }
+  }
+  // (block-uniform condition; like the stand-alone rotary kernel, a position outside the table
+  // leaves the cache untouched)
+  if (ap.k_new != nullptr && pos >= key_begin && pos < key_end && (ap.cos_tab == nullptr || rotate)) {
+    const int64_t src = (int64_t)b * ap.kv_batch_stride + (int64_t)hkv * D;
+    const int64_t dst = (int64_t)b * cache_batch_stride + (int64_t)pos * cache_row_stride + (int64_t)hkv * D;
+    uint16_t* kc = const_cast<uint16_t*>(k_cache);
+    uint16_t* vc = const_cast<uint16_t*>(v_cache);
+    if (tid < D / 2) {
+      const float a = bits_to_f32<BF16>(ap.k_new[src + tid]), bb = bits_to_f32<BF16>(ap.k_new[src + tid + D / 2]);
+      float c = 1.f, sn = 0.f;
+      if (rotate) {
+        c = ap.cos_tab[(int64_t)pos * (D / 2) + tid];
+        sn = ap.sin_tab[(int64_t)pos * (D / 2) + tid];
+      }
+      kc[dst + tid] = rotate ? f32_to_bits<BF16>(a * c - bb * sn) : ap.k_new[src + tid];
+      kc[dst + tid + D / 2] = rotate ? f32_to_bits<BF16>(a * sn + bb * c) : ap.k_new[src + tid + D / 2];
+    } else if (tid < D / 2 + D / 8) {
+      const int i = (tid - D / 2) * 8;
+      *reinterpret_cast<uint4*>(vc + dst + i) = *reinterpret_cast<const uint4*>(ap.v_new + src + i);
+    }
+    __syncthreads();                               // the row is in place before any warp of the block fetches it
   }
 
   float o[NH][8][4];
@@ -376,7 +446,7 @@ __global__ void kv_append_kernel(uint4* __restrict__ k_cache, uint4* __restrict_
 template <bool BF16, int D>
 int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, int64_t bs, int64_t rs,
                   const int32_t* seqlens, void* out, int8_t* out_q, float* out_scale, int B, int Hq, int Hkv,
-                  int max_seqlen, float softcap, void* workspace, cudaStream_t st) {
+                  int max_seqlen, float softcap, void* workspace, cudaStream_t st, const DecodeAppend& ap) {
   // Keys per block: the smallest power of two for which all blocks are resident at once (two fit an
   // SM), i.e. as many blocks as one wave takes and no second wave -- a block costs about 3 us beyond
   // its keys (first loads, merge of its warps), so waves of short blocks lose to one wave of long
@@ -411,7 +481,7 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
                               reinterpret_cast<const uint16_t*>(q), qbs, reinterpret_cast<const uint16_t*>(kc),
                               reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
-                              Hq, Hkv, chunk, max_splits, scale, softcap, part_o, part_ml))
+                              Hq, Hkv, chunk, max_splits, scale, softcap, part_o, part_ml, ap))
     return rc;
   if (int rc = check_launch("attn_decode")) return rc;
   if (need_merge) {
@@ -454,10 +524,11 @@ int llmqrt_kv_append(void* k_cache, void* v_cache, int64_t cache_batch_stride, i
   return check_launch("kv_append");
 }
 
-int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
-                       int64_t cache_batch_stride, int64_t cache_row_stride, const int32_t* seqlens, void* out,
-                       int8_t* out_q, float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
-                       int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream) {
+static int attn_decode_entry(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                             int64_t cache_batch_stride, int64_t cache_row_stride, const int32_t* seqlens, void* out,
+                             int8_t* out_q, float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
+                             int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream,
+                             const DecodeAppend& ap) {
   LLMQRT_REQUIRE(dtype == LLMQRT_F16 || dtype == LLMQRT_BF16, "attn_decode: dtype must be fp16 or bf16");
   LLMQRT_REQUIRE(d == 64 || d == 128, "attn_decode: head_dim must be 64 or 128 (got %lld)", (long long)d);
   LLMQRT_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8, "attn_decode: need Hq %% Hkv == 0 and at most 8 query heads per KV head");
@@ -475,10 +546,39 @@ int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cach
 #define LLMQRT_GO(BF, DD)                                                                                          \
   return launch_decode<BF, DD>(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, cache_row_stride, seqlens, \
                                out, out_q, out_scale, (int)B, (int)Hq, (int)Hkv, (int)max_seqlen, softcap,         \
-                               workspace, st)
+                               workspace, st, ap)
   if (d == 128) { if (bf) LLMQRT_GO(true, 128); else LLMQRT_GO(false, 128); }
   if (bf) LLMQRT_GO(true, 64); else LLMQRT_GO(false, 64);
 #undef LLMQRT_GO
+}
+
+int llmqrt_attn_decode(const void* q, int64_t q_batch_stride, const void* k_cache, const void* v_cache,
+                       int64_t cache_batch_stride, int64_t cache_row_stride, const int32_t* seqlens, void* out,
+                       int8_t* out_q, float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
+                       int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream) {
+  const DecodeAppend none = {nullptr, nullptr, 0, nullptr, nullptr, 0};
+  return attn_decode_entry(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, cache_row_stride, seqlens, out,
+                           out_q, out_scale, dtype, B, Hq, Hkv, d, max_seqlen, softcap, workspace, stream, none);
+}
+
+int llmqrt_attn_decode_append(const void* q, int64_t q_batch_stride, const void* k_new, const void* v_new,
+                              int64_t kv_batch_stride, const float* cos_table, const float* sin_table,
+                              int64_t table_rows, void* k_cache, void* v_cache, int64_t cache_batch_stride,
+                              int64_t cache_row_stride, const int32_t* seqlens, void* out, int8_t* out_q,
+                              float* out_scale, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t d,
+                              int64_t max_seqlen, float softcap, void* workspace, llmqrt_stream_t stream) {
+  LLMQRT_REQUIRE((k_new == nullptr) == (v_new == nullptr), "attn_decode_append: k_new and v_new go together");
+  LLMQRT_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "attn_decode_append: cos and sin tables go together");
+  LLMQRT_REQUIRE(!k_new || (kv_batch_stride >= Hkv * d && kv_batch_stride % 8 == 0 &&
+                            ((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new)) & 15) == 0),
+                 "attn_decode_append: k_new / v_new must be 16-byte aligned with a batch stride that is a multiple of 8");
+  LLMQRT_REQUIRE(!cos_table || (table_rows > 0 && table_rows <= 0x7fffffffll &&
+                                ((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table)) & 7) == 0),
+                 "attn_decode_append: rotary tables must be 8-byte aligned fp32 [table_rows, d/2]");
+  const DecodeAppend ap = {static_cast<const uint16_t*>(k_new), static_cast<const uint16_t*>(v_new),
+                           (long long)kv_batch_stride, cos_table, sin_table, (int)table_rows};
+  return attn_decode_entry(q, q_batch_stride, k_cache, v_cache, cache_batch_stride, cache_row_stride, seqlens, out,
+                           out_q, out_scale, dtype, B, Hq, Hkv, d, max_seqlen, softcap, workspace, stream, ap);
 }
 
 }  // extern "C"

@@ -165,15 +165,17 @@ class Qwen2Decoder:
             qkv4 = qkv.view(B, S, self.hq + 2 * self.hkv, d)
             q, k, v = qkv4[:, :, :self.hq], qkv4[:, :, self.hq:self.hq + self.hkv], qkv4[:, :, self.hq + self.hkv:]
             kc, vc = L_.k_cache[batch0:batch0 + B], L_.v_cache[batch0:batch0 + B]
-            glue.rope_kv_write(q, k, v, self.cos, self.sin, pos0=self.pos, pos_dev=self.pos_dev if decode else None,
-                               k_cache=kc, v_cache=vc)
             if decode:
-                # q is read in place from the fused projection output; the split-merge kernel also
-                # emits the per-token int8 row that the output projection consumes
+                # One kernel: q, k, v are read in place from the fused projection output, q and k are
+                # rotated at the row's angle (seqlens == position + 1), k and v go into the cache,
+                # and the kernel that finishes the attention also emits the per-token int8 row that
+                # the output projection consumes.
                 _, aq, a_s = attention.attn_decode(q[:, 0], kc, vc, self.seqlens[batch0:batch0 + B],
                                                    self.max_seq_len if self._capturing else self.pos + 1,
-                                                   quantize=True)
+                                                   quantize=True, k_new=k[:, 0], v_new=v[:, 0],
+                                                   cos=self.cos, sin=self.sin)
             else:
+                glue.rope_kv_write(q, k, v, self.cos, self.sin, pos0=self.pos, pos_dev=None, k_cache=kc, v_cache=vc)
                 attn = attention.flash_attn_func(q, k, v, causal=True)
                 aq, _, a_s = ops.quantize_int8(attn.reshape(B * S, nq), per_token=True)
             o = ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt)

@@ -136,6 +136,43 @@ def test_decode_strided_q_and_fused_quantization(dtype, lens):
     assert torch.equal(out_q.cpu(), q_ref) and torch.equal(scale.cpu(), s_ref.float().reshape(-1))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,d,lens,Smax", [(28, 4, 128, [1100, 1, 300, 513], 1200), (14, 2, 64, [64, 7, 33], 64),
+                                                 (3, 1, 128, [5000, 4097], 5100)])
+def test_decode_with_rotary_and_append_in_kernel(dtype, Hq, Hkv, d, lens, Smax):
+    # rotary + cache write folded into the attention kernel == rope_kv_write kernel, then attention
+    from llmqrt_b200 import glue
+    from llmqrt_b200.attention import attn_decode, flash_attn_with_kvcache
+    B = len(lens)
+    g = torch.Generator().manual_seed(21)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * d, generator=g).to(dtype).cuda()
+    kc0 = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()
+    vc0 = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()
+    seqlens = torch.tensor(lens, dtype=torch.int32, device="cuda")                 # lengths INCLUDING the new token
+    cos, sin = glue.rope_tables(d, Smax, 1e6, "cuda")
+    rows = qkv.view(B, Hq + 2 * Hkv, d)
+    # reference chain, one sequence at a time (the stand-alone rotary kernel takes one position per call)
+    kc_ref, vc_ref = kc0.clone(), vc0.clone()
+    q_rot = torch.empty(B, Hq, d, dtype=dtype, device="cuda")
+    for b, L_b in enumerate(lens):
+        r = rows[b:b + 1].unsqueeze(1).clone()                                     # [1, 1, heads, d]
+        q1, k1, v1 = r[:, :, :Hq], r[:, :, Hq:Hq + Hkv], r[:, :, Hq + Hkv:]
+        glue.rope_kv_write(q1, k1, v1, cos, sin, pos0=L_b - 1, k_cache=kc_ref[b:b + 1], v_cache=vc_ref[b:b + 1])
+        q_rot[b] = q1[0, 0]
+    want = attn_decode(q_rot, kc_ref, vc_ref, seqlens, Smax)
+    kc, vc = kc0.clone(), vc0.clone()
+    got, got_q, got_s = attn_decode(rows[:, :Hq], kc, vc, seqlens, Smax, quantize=True, k_new=rows[:, Hq:Hq + Hkv],
+                                    v_new=rows[:, Hq + Hkv:], cos=cos, sin=sin)
+    assert bits_equal(kc, kc_ref) and bits_equal(vc, vc_ref)                       # same rotation arithmetic, same rows
+    assert bits_equal(got, want)
+    # the flash-attn spelling of the same call: cache_seqlens are the lengths BEFORE the append
+    kc2, vc2 = kc0.clone(), vc0.clone()
+    out2 = flash_attn_with_kvcache(rows[:, :Hq].unsqueeze(1), kc2, vc2, k=rows[:, Hq:Hq + Hkv].unsqueeze(1),
+                                   v=rows[:, Hq + Hkv:].unsqueeze(1), rotary_cos=cos, rotary_sin=sin,
+                                   cache_seqlens=seqlens - 1, rotary_interleaved=False, max_seqlen_k=Smax)
+    assert bits_equal(out2[:, 0], got) and bits_equal(kc2, kc)
+
+
 def test_decode_quantization_single_split_without_workspace():
     # short caches need no split partials, hence no workspace; the merge kernel still quantizes the rows
     from llmqrt_b200 import _lib as L
