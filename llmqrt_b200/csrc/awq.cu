@@ -213,13 +213,33 @@ awq_gemm_stream_kernel(const __half* __restrict__ X, int64_t ldx, const uint32_t
   __syncthreads();
   if (s_ticket != num_splits - 1) return;
   __threadfence();
+  // N is a multiple of 8: four columns per thread, slices four at a time (independent loads, so the
+  // fix-up costs a few L2 round trips instead of one per slice and element)
   const int nb0 = blockIdx.x * kRowsPerBlock;
-  for (int i = tid; i < M * kRowsPerBlock; i += kThreads) {
-    const int m = i / kRowsPerBlock, n = nb0 + (i % kRowsPerBlock);
+  constexpr int kVecs = kRowsPerBlock / 4;
+  if (M < 4) {                                     // too few rows to keep every thread busy with vectors
+    for (int i = tid; i < M * kRowsPerBlock; i += kThreads) {
+      const int m = i / kRowsPerBlock, n = nb0 + (i % kRowsPerBlock);
+      if (n >= N) continue;
+      float sum = 0.f;
+#pragma unroll 4
+      for (int s = 0; s < num_splits; ++s) sum += __ldcg(partials + ((int64_t)s * M + m) * N + n);
+      epilogue_store<float>(epi, sum, m, n, alpha);
+    }
+    if (tid == 0) counters[blockIdx.x] = 0;
+    return;
+  }
+  for (int i = tid; i < M * kVecs; i += kThreads) {
+    const int m = i / kVecs, n = nb0 + (i % kVecs) * 4;
     if (n >= N) continue;
-    float sum = 0.f;
-    for (int s = 0; s < num_splits; ++s) sum += __ldcg(partials + ((int64_t)s * M + m) * N + n);
-    epilogue_store<float>(epi, sum, m, n, alpha);
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int s = 0; s < num_splits; ++s) {
+      const float4 p = __ldcg(reinterpret_cast<const float4*>(partials + ((int64_t)s * M + m) * N + n));
+      sum[0] += p.x; sum[1] += p.y; sum[2] += p.z; sum[3] += p.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) epilogue_store<float>(epi, sum[j], m, n + j, alpha);
   }
   if (tid == 0) counters[blockIdx.x] = 0;
 }
@@ -229,7 +249,10 @@ int launch_gemm(const __half* X, int64_t ldx, const uint32_t* wq_t, const uint32
                 const Epilogue& epi, void* workspace, cudaStream_t st) {
   const int n_blocks = (int)ceil_div(N, kRowsPerBlock);
   const int max_kps_smem = ((96 * 1024) / (MB * 8) - 16) / 2 / kChunkK * kChunkK;
+  // enough blocks to cover every SM about four times, but at most 16 slices: the block that arrives
+  // last adds them all, and that serial tail outweighs finer slices
   int want_splits = (int)ceil_div(4 * sm_count(), n_blocks);
+  if (want_splits > 16) want_splits = 16;
   int kps = (int)ceil_div(ceil_div(K, want_splits), kChunkK) * kChunkK;
   if (kps < 256) kps = 256;
   if (kps > max_kps_smem) kps = max_kps_smem;

@@ -139,12 +139,34 @@ w8a8_stream_kernel(const uint8_t* __restrict__ A, int64_t lda, const uint8_t* __
   __threadfence();
 
   const int nb0 = blockIdx.x * kRowsPerBlock;
-  for (int i = tid; i < M * kRowsPerBlock; i += kThreads) {
-    const int m = i / kRowsPerBlock, n = nb0 + (i % kRowsPerBlock);
-    if (n >= N) continue;
-    Acc sum = 0;
-    for (int s = 0; s < num_splits; ++s) sum += __ldcg(part + ((int64_t)s * M + m) * N + n);
-    epilogue_store<Acc>(epi, sum, m, n, alpha);
+  if ((N & 3) == 0 && M >= 4) {
+    // enough rows to keep every thread busy with vectors: four columns per thread and the slices
+    // four at a time -- the loads of a thread do not depend on one another, so the fix-up costs a
+    // few L2 round trips instead of one per slice and element
+    constexpr int kVecs = kRowsPerBlock / 4;
+    for (int i = tid; i < M * kVecs; i += kThreads) {
+      const int m = i / kVecs, n = nb0 + (i % kVecs) * 4;
+      if (n >= N) continue;
+      Acc sum[4] = {0, 0, 0, 0};
+#pragma unroll 4
+      for (int s = 0; s < num_splits; ++s) {
+        const uint4 p = __ldcg(reinterpret_cast<const uint4*>(part + ((int64_t)s * M + m) * N + n));
+        const Acc* pv = reinterpret_cast<const Acc*>(&p);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sum[j] += pv[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) epilogue_store<Acc>(epi, sum[j], m, n + j, alpha);
+    }
+  } else {
+    for (int i = tid; i < M * kRowsPerBlock; i += kThreads) {
+      const int m = i / kRowsPerBlock, n = nb0 + (i % kRowsPerBlock);
+      if (n >= N) continue;
+      Acc sum = 0;
+#pragma unroll 4
+      for (int s = 0; s < num_splits; ++s) sum += __ldcg(part + ((int64_t)s * M + m) * N + n);
+      epilogue_store<Acc>(epi, sum, m, n, alpha);
+    }
   }
   if (tid == 0) counters[blockIdx.x] = 0;            // leave the workspace ready for the next call
 }
@@ -157,6 +179,7 @@ int launch(const uint8_t* A, int64_t lda, const uint8_t* W, int64_t ldw, int M, 
   // bytes, and an activation slice that fits in 96 KiB of shared memory.
   const int max_kps_smem = ((96 * 1024) / (MB * 8) - 64) / 64 * 64;
   int want_splits = (int)ceil_div(3 * sm_count(), n_blocks);
+  if (want_splits > 16) want_splits = 16;            // the last block adds all slices: keep that tail short
   int kps = (int)ceil_div(ceil_div(K, want_splits), 64) * 64;
   if (kps < 256) kps = 256;
   if (kps > max_kps_smem) kps = max_kps_smem;
@@ -272,6 +295,7 @@ int launch_noalloc(const uint8_t* A, int64_t lda, const uint8_t* W, int64_t ldw,
   // Same decomposition rule as the regular path, with the partial sums limited to the built-in array.
   const int max_kps_smem = ((96 * 1024) / (MB * 8) - 64) / 64 * 64;
   int want_splits = (int)ceil_div(3 * sm_count(), n_blocks);
+  if (want_splits > 16) want_splits = 16;            // the last block adds all slices: keep that tail short
   int kps = (int)ceil_div(ceil_div(K, want_splits), 64) * 64;
   if (kps < 256) kps = 256;
   if (kps > max_kps_smem) kps = max_kps_smem;

@@ -259,7 +259,6 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
 
 #ifdef LLMQRT_TIMELINE
 __device__ unsigned long long g_last_done;   // latest exit time over the blocks of the launch in flight
-__device__ unsigned long long g_cta_times[4][512];   // per block of the latest N == K == 3584 launch: enter, dependency met, accumulator done, exit
 #endif
 
 template <int KIND, int BN>
@@ -301,7 +300,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
 #ifdef LLMQRT_TIMELINE
     for (int i = 0; i < 16; ++i) tr_clk[i] = 0;
     if (blockIdx.x == 0) tr_prev_last_done = atomicExch(&g_last_done, 0ull);
-    if (prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[0][blockIdx.x] = tc::global_timer_ns();
 #endif
     TC_TRACE(11);
     TC_TRACE(0);
@@ -383,9 +381,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           // queue behind the prefetches.)
           pdl_wait();
           TC_TRACE(12);
-#ifdef LLMQRT_TIMELINE
-          if (prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[1][blockIdx.x] = tc::global_timer_ns();
-#endif
           pdl_trigger();
         }
       }
@@ -468,9 +463,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         if (*abort) { ok = false; break; }
         tc::mma_commit(tc::smem_u32(&bar_acc_full[buf]));        // accumulator complete
         TC_TRACE(3);
-#ifdef LLMQRT_TIMELINE
-        if (prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[2][blockIdx.x] = tc::global_timer_ns();
-#endif
         acc_phase[buf] ^= 1u;
         buf ^= 1;
       }
@@ -630,7 +622,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     }
   }
   if (threadIdx.x == 0) atomicMax(&g_last_done, tc::global_timer_ns());
-  if (threadIdx.x == 0 && prm.N == 3584 && prm.k_blocks == 28 && blockIdx.x < 512) g_cta_times[3][blockIdx.x] = tc::global_timer_ns();
 #endif
   if (warp == 1) {
     tc::fence_after_sync();
@@ -806,8 +797,3 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
 }  // namespace llmqrt
 
 LLMQRT_TIMELINE_DUMP(gemm)
-#ifdef LLMQRT_TIMELINE
-extern "C" int llmqrt_timeline_gemm_blocks(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, llmqrt::g_cta_times, sizeof(unsigned long long) * 4 * 512) == cudaSuccess ? 0 : -1;
-}
-#endif
