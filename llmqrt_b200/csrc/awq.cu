@@ -148,21 +148,34 @@ awq_gemm_stream_kernel(const __half* __restrict__ X, int64_t ldx, const uint32_t
     for (int r = 0; r < 4; ++r) rows[r] = min(n0 + 16 * (r >> 1) + g + 8 * (r & 1), N - 1);
     const int my_len = k_len - 32 * t;
 
-    for (int kc = 0; kc < k_len; kc += kChunkK) {
-      uint4 wv[4];
-      uint32_t szv[4];
+    // The weights of step kc + 1 are requested before step kc is consumed (two register sets), so a
+    // block's steps overlap their load latency instead of paying it one after the other.
+    uint4 wnext[4];
+    uint32_t sznext[4];
+    auto fetch = [&](int kc) {
       const bool valid = kc < my_len;
       const int kk = k_begin + kc + 32 * t;       // first k of this lane's 32 values
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         if (valid) {
-          wv[r] = ldg_stream_16B(wq_t + (int64_t)rows[r] * KW + kk / 8);
-          szv[r] = __ldg(sz_t + (int64_t)rows[r] * KG + kk / G);
+          wnext[r] = ldg_stream_16B(wq_t + (int64_t)rows[r] * KW + kk / 8);
+          sznext[r] = __ldg(sz_t + (int64_t)rows[r] * KG + kk / G);
         } else {
-          wv[r] = make_uint4(0, 0, 0, 0);
-          szv[r] = 0;                               // scale 0: contributes nothing
+          wnext[r] = make_uint4(0, 0, 0, 0);
+          sznext[r] = 0;                            // scale 0: contributes nothing
         }
       }
+    };
+    fetch(0);
+    for (int kc = 0; kc < k_len; kc += kChunkK) {
+      uint4 wv[4];
+      uint32_t szv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        wv[r] = wnext[r];
+        szv[r] = sznext[r];
+      }
+      if (kc + kChunkK < k_len) fetch(kc + kChunkK);
       const uint32_t* wp[4] = {&wv[0].x, &wv[1].x, &wv[2].x, &wv[3].x};
 #pragma unroll
       for (int wi = 0; wi < 4; ++wi) {

@@ -759,6 +759,26 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   LLMQRT_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0,
                  "tcgen05 gemm: operands must be 16-byte aligned");
 
+  // A mid-sized M with a narrow N has only a handful of 128 x 256 tiles, and that schedule has no
+  // split-K: most SMs would idle (M = 256, N = 1536, K = 8960: 12 tiles, 76 us; as panels 42 us).  Such problems run as
+  // panels of 128 rows through the small-M schedule, whose cluster split-K fills the machine; the
+  // weights of the second and later panels come from L2.
+  if (M > 128 && M <= 1024) {
+    const int64_t tiles = ceil_div(M, (int64_t)kBM) * ceil_div(N, (int64_t)(N <= 128 ? 128 : 256));
+    if (tiles * 4 <= sm_count()) {
+      const int64_t out_es = epi.mode == EPI_RAW ? 4 : 2;
+      for (int64_t m0 = 0; m0 < M; m0 += kBM) {
+        Epilogue e = epi;
+        e.out = static_cast<char*>(epi.out) + m0 * epi.ldo * out_es;
+        if (e.row_scale) e.row_scale += m0;
+        const int64_t rows = M - m0 < kBM ? M - m0 : kBM;
+        if (int rc = gemm_tc(kind, static_cast<const char*>(A) + m0 * lda * elt, lda, W, ldw, rows, N, K, e, workspace, st))
+          return rc;
+      }
+      return LLMQRT_OK;
+    }
+  }
+
   TcParams prm{};
   prm.M = (int)M;
   prm.N = (int)N;
