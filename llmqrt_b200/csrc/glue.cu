@@ -551,7 +551,7 @@ int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* 
   // Register-resident variant: the smallest cluster whose slices fit one block (8 elements per
   // thread), widened while that still leaves every SM at most a few blocks and slices of >= 128 threads.
   int rcl = 0;
-  if (vec) {
+  if (vec && M <= 1024) {                            // (prefill-sized M: the staged kernel streams better)
     const int64_t units = I / 8;
     for (int c = 1; c <= 8; c *= 2)
       if (units % c == 0 && units / c <= 1024) { rcl = c; break; }

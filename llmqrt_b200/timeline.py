@@ -70,6 +70,7 @@ def main():
     model.decode_step(tok)
     torch.cuda.synchronize()
     ev = _dump(_lib._lib, True)
+    ev = [e for e in ev if e[1] != 4 or e[0] >= min(t for t, i in ev if i != 4)]   # drop the previous step's last-block mark
     t0 = ev[0][0]
     print(f"{len(ev)} marks over {(ev[-1][0] - t0) / 1e3:.1f} us (one decode step, batch {args.batch}, context {args.prompt_len + 7})")
     ready = [(t, NAMES[i]) for t, i in ev if NAMES.get(i, "").endswith("ready")]
