@@ -88,6 +88,10 @@ int llmqrt_quantize_fp8_static(const void* x, int x_dtype, int64_t M, int64_t K,
  * W8A8 GEMMs.   acc[m, n] = sum_k a[m, k] * w[n, k]
  * Requirements: K % 16 == 0, lda % 16 == 0, ldw % 16 == 0, 16-byte aligned a and w.
  * `alpha_dev`, when not NULL, is a device fp32 scalar used instead of `alpha`.
+ * `w` is a stored weight: the kernels may start reading it before the kernel that precedes the
+ * call on `stream` has finished (they only wait for that kernel before touching `a`, the scales
+ * and `out`), so `w` must not be produced by that preceding kernel.  llmqrt_gemm_16bit makes no
+ * such assumption.
  * ---------------------------------------------------------------------------------------- */
 
 /* int8 x int8 -> exact int32 accumulators -> out fp16 = alpha * acc + beta * bias[n].

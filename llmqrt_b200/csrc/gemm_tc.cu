@@ -12,15 +12,18 @@
 // Split-K for skinny problems: when there are fewer tiles than SMs, the reduction dimension of a tile
 // is divided among the 2, 4 or 8 CTAs of a thread-block CLUSTER.  Each CTA accumulates its K range in
 // tensor memory, then the cluster reduce-scatters through distributed shared memory: CTA r owns
-// BN/S accumulator columns, every CTA stores its slice of those columns straight into r's shared
-// memory, and after one cluster barrier r adds the S contributions in rank order (deterministic) and
-// runs the epilogue.  No global scratch, no atomics, no second kernel.
+// BN/S accumulator columns, every CTA bulk-copies its slice of those columns into r's shared memory
+// after one cluster barrier, r adds the S contributions in rank order (deterministic) and runs the
+// epilogue; peers are released by remote mbarrier arrivals instead of a second cluster barrier.  No
+// global scratch, no atomics, no second kernel.
+//
+// Launched with programmatic dependent launch: the block's first ring of WEIGHT tiles is requested
+// before griddepcontrol.wait (weights are constants of the model), the activation tiles after it.
 //
 // Warp roles (192 threads): warp 0 lane 0 issues TMA; warp 1 owns tensor memory and its lane 0
 // issues the MMAs; warps 2-5 run the epilogue (TMEM lane quadrant = warp id % 4).  All waits on
 // mbarriers are bounded; a time-out raises a block-wide abort flag and a status word in the
-// workspace, every role drains, reaches the cluster barriers and the block frees its tensor memory
-// before returning.
+// workspace, every role drains and the block frees its tensor memory before returning.
 //
 // Epilogue: accumulators go TMEM -> registers, the scales / bias are applied there (the per-column
 // ones come from a small shared-memory vector loaded once per tile), the 16-bit results are staged in
@@ -359,7 +362,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       // first work item is requested BEFORE waiting for the preceding kernel of the stream; the
       // activation tiles of the same stages follow after the wait and complete the same barriers.
       // On a programmatic launch this streams up to a ring of weights per SM while the preceding
-      // kernel is still running.
+      // kernel is still running.  Only for the 8-bit kinds, whose W is by contract a stored weight:
+      // the 16-bit GEMM is also handed matrices that the preceding kernel has just produced (an AWQ
+      // layer dequantized for a large M), so it waits first.
+      constexpr bool kEarlyWeights = KIND != tc::MMA_F16;
+      if (!kEarlyWeights) {
+        pdl_wait();
+        TC_TRACE(12);
+        pdl_trigger();
+      }
       const int pre = first_tile < num_tiles ? min(kStages, kb_count) : 0;
       for (int phase_w = 1; phase_w >= 0; --phase_w) {     // 1: weights, 0: activations
         const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
@@ -375,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           if (load_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
           else tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
         }
-        if (phase_w) {
+        if (phase_w && kEarlyWeights) {
           // (Prefetching further weight tiles into L2 here was measured to slow the kernel down: the
           // ring already keeps more bytes in flight than HBM needs, and the activation loads then
           // queue behind the prefetches.)

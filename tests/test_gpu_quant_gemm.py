@@ -90,6 +90,9 @@ INT8_SHAPES = [
     (1, 896, 896), (7, 128, 896), (16, 896, 4864), (64, 4864, 896),
     (1, 8, 16), (3, 130, 48), (17, 1000, 208), (33, 72, 1040), (64, 3584, 3584),
     (128, 512, 1024), (200, 384, 512), (1024, 896, 896), (300, 1000, 4864),
+    # per-rank shards of the Qwen2-7B linears at tensor-parallel 4 and 8 (batch 64): narrow N, short
+    # or ragged K (2368 = 18.5 blocks of 128 bytes), and the 128-row panel schedule (M = 256, few tiles)
+    (64, 768, 3584), (64, 3584, 384), (64, 4736, 3584), (64, 3584, 2368), (64, 3584, 896), (256, 1536, 2368),
 ]
 
 
