@@ -215,6 +215,50 @@ __device__ __forceinline__ void epi_stage_group8(const TcParams& prm, const EpiC
   }
 }
 
+// The same for the case every decode step runs four times per layer -- swapped roles, scaled epilogue,
+// 16-bit output -- with the run-time choices of the general version (mode, order of the two scales,
+// bias, output type) made once per group instead of once per element: the epilogue of a narrow GEMM
+// is a short single pass per block, bound by its instruction count.
+template <typename AccT, bool BF16, bool VAR_FIRST, bool HAS_BIAS>
+__device__ __forceinline__ void epi_stage_group8_swap16(const EpiConsts& ec, const uint32_t (&r)[8],
+                                                        const float* q_scale, int c, int et, uint8_t* stage) {
+  constexpr int pitch = kBM * 2 + 16;                  // stage_pitch(swap = true, es = 2)
+  const float4 s0 = *reinterpret_cast<const float4*>(q_scale), s1 = *reinterpret_cast<const float4*>(q_scale + 4);
+  const float qs[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  uint8_t* p = stage + c * pitch + et * 2;             // element jj goes to staged row c + jj, column et
+#pragma unroll
+  for (int jj = 0; jj < 8; ++jj) {
+    const float acc = (float)acc_from_bits<AccT>(r[jj]);
+    float v = VAR_FIRST ? __fmul_rn(__fmul_rn(acc, qs[jj]), ec.fix_scale) : __fmul_rn(__fmul_rn(acc, ec.fix_scale), qs[jj]);
+    if (HAS_BIAS) v = __fadd_rn(v, ec.fix_bias);       // swapped roles: the bias belongs to this lane's channel
+    uint16_t bits;
+    if constexpr (BF16) bits = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    else bits = __half_as_ushort(__float2half_rn(v));
+    *reinterpret_cast<uint16_t*>(p + jj * pitch) = bits;
+  }
+}
+
+template <typename AccT>
+__device__ __forceinline__ void epi_stage_group8_any(const TcParams& prm, const EpiConsts& ec, const uint32_t (&r)[8],
+                                                     const float* q_scale, const float* q_bias, int c, int et,
+                                                     uint8_t* stage) {
+  const Epilogue& e = prm.epi;
+  if (prm.swap && (e.mode == EPI_ROW_COL || e.mode == EPI_COL_ROW) && e.out_dtype != LLMQRT_F32) {
+    const int sel = (e.out_dtype == LLMQRT_BF16 ? 4 : 0) | (ec.var_first ? 2 : 0) | (ec.has_bias ? 1 : 0);
+    switch (sel) {
+      case 0: return epi_stage_group8_swap16<AccT, false, false, false>(ec, r, q_scale, c, et, stage);
+      case 1: return epi_stage_group8_swap16<AccT, false, false, true>(ec, r, q_scale, c, et, stage);
+      case 2: return epi_stage_group8_swap16<AccT, false, true, false>(ec, r, q_scale, c, et, stage);
+      case 3: return epi_stage_group8_swap16<AccT, false, true, true>(ec, r, q_scale, c, et, stage);
+      case 4: return epi_stage_group8_swap16<AccT, true, false, false>(ec, r, q_scale, c, et, stage);
+      case 5: return epi_stage_group8_swap16<AccT, true, false, true>(ec, r, q_scale, c, et, stage);
+      case 6: return epi_stage_group8_swap16<AccT, true, true, false>(ec, r, q_scale, c, et, stage);
+      default: return epi_stage_group8_swap16<AccT, true, true, true>(ec, r, q_scale, c, et, stage);
+    }
+  }
+  epi_stage_group8<AccT>(prm, ec, r, q_scale, q_bias, c, et, stage);
+}
+
 // Phase 2: staged block D[i0 .. i0+128, j0 .. j0+ncols) -> global memory, 16 bytes per thread and step.
 __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8_t* stage, int ncols, int i0, int j0,
                                                 int t) {
@@ -516,7 +560,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           uint32_t r[8];
           tc::tmem_ld_32x8(taddr + (uint32_t)(c0 + c), r);
           tc::tmem_ld_wait();
-          epi_stage_group8<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
+          epi_stage_group8_any<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
         epi_barrier();
         epi_drain_chunk(prm, stage, min(kChunk, prm.rows_q - j0), tp * kBM, j0, et);
@@ -546,13 +590,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     const EpiConsts& ec = ec_split;                    // q_scale / q_bias cover only the columns this CTA owns
     if (warp >= 2 && healthy) {
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      // 32 columns per round trip to tensor memory (four loads in flight before the wait): the
+      // wait, not the data volume, is what each round costs
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 8) {
-        uint32_t r[8];
-        tc::tmem_ld_32x8(taddr + (uint32_t)c0, r);
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[4][8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) tc::tmem_ld_32x8(taddr + (uint32_t)(c0 + 8 * q), r[q]);
         tc::tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) send[(c0 + jj) * kBM + et] = r[jj];
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) send[(c0 + 8 * q + jj) * kBM + et] = r[q][jj];
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> bulk-copy reads
       if (threadIdx.x == 64) TC_TRACE(7);
@@ -604,7 +653,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           uint32_t r[8];
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) r[jj] = acc_to_bits<AccT>(sum[jj]);
-          epi_stage_group8<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
+          epi_stage_group8_any<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
         epi_barrier();
         epi_drain_chunk(prm, stage, ncols, tp * kBM, j0, et);

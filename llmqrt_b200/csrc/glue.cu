@@ -9,6 +9,7 @@
 // decode step this spreads the work over every SM instead of 64 of them.  128-bit accesses whenever
 // the slice is 16-byte aligned; the computed slice stays in shared memory for the quantization pass.
 #include <cooperative_groups.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "peer_comm.cuh"
@@ -347,7 +348,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __restrict__ x, T* __restrict__ x_out,
                          const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
-                         float* __restrict__ scale_f32, int64_t H) {
+                         float* __restrict__ scale_f32, int64_t H, int two_step) {
   LLMQRT_TIMELINE_MARK(10);
   pdl_trigger_then_wait();
   LLMQRT_TIMELINE_MARK(11);
@@ -368,11 +369,22 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
       // Word placement (any bijection works, as every rank uses the same one): the two words of a
       // thread sit 32 words apart so that each store or poll of a warp covers 512 contiguous bytes.
       const long long word = m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31), word1 = word + 32;
-      comm_push(c, seq, word, make_uint2(pv.x, pv.y));
-      comm_push(c, seq, word1, make_uint2(pv.z, pv.w));
+      // One step: every rank sends its row to every rank and all add the W copies themselves (W x the
+      // payload leaves each rank).  Two steps, for many ranks: a row goes only to the rank that owns
+      // it (rows are dealt out in equal runs), the owner adds the copies and sends the finished row,
+      // rounded to T, to everyone (2 x the payload leaves each rank, one more hop of latency).
+      const int rows_per_rank = ((int)gridDim.x + c.world - 1) / c.world;
+      const int owner = two_step ? min((int)(m / rows_per_rank), c.world - 1) : c.rank;
+      if (two_step) {
+        comm_push_one(c, seq, owner, c.rank, word, make_uint2(pv.x, pv.y));
+        comm_push_one(c, seq, owner, c.rank, word1, make_uint2(pv.z, pv.w));
+      } else {
+        comm_push(c, seq, word, make_uint2(pv.x, pv.y));
+        comm_push(c, seq, word1, make_uint2(pv.z, pv.w));
+      }
       const unsigned long long t0 = comm_timer_ns();
       bool ok = true;
-      for (int s = 0; s < c.world && ok; ++s) {
+      for (int s = 0; s < c.world && ok && owner == c.rank; ++s) {
         uint2 d0, d1;
         ok = comm_gather(c, seq, s, word, t0, &d0) && comm_gather(c, seq, s, word1, t0, &d1);
         if (ok) {
@@ -383,6 +395,27 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
             acc[j] += to_f32<T>(e0[j]);
             acc[4 + j] += to_f32<T>(e1[j]);
           }
+        }
+      }
+      if (two_step) {
+        if (owner == c.rank && ok) {
+          __align__(16) T red[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) red[j] = from_f32<T>(acc[j]);
+          const uint4 rv = *reinterpret_cast<const uint4*>(red);
+          for (int p = 0; p < c.world; ++p) {
+            comm_push_one(c, seq, p, kCommMaxWorld, word, make_uint2(rv.x, rv.y));
+            comm_push_one(c, seq, p, kCommMaxWorld, word1, make_uint2(rv.z, rv.w));
+          }
+        }
+        uint2 d0, d1;
+        ok = ok && comm_gather(c, seq, kCommMaxWorld, word, t0, &d0) && comm_gather(c, seq, kCommMaxWorld, word1, t0, &d1);
+        const T* e0 = reinterpret_cast<const T*>(&d0);
+        const T* e1 = reinterpret_cast<const T*>(&d1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[j] = ok ? to_f32<T>(e0[j]) : 0.f;
+          acc[4 + j] = ok ? to_f32<T>(e1[j]) : 0.f;
         }
       }
     }
@@ -526,12 +559,18 @@ int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x
   for (int p = 0; p < c->dev.world; ++p)
     LLMQRT_REQUIRE(c->dev.base[p] != nullptr, "comm_allreduce_rmsnorm: peer %d has not been opened", p);
   const unsigned threads = (unsigned)(((H / 8) + 31) / 32 * 32);
+  // two steps from 8 ranks on (or when LLMQRT_ALLREDUCE_TWO_STEP=1 asks for it, e.g. to test on fewer)
+  static const bool force_two_step = [] {
+    const char* v = getenv("LLMQRT_ALLREDUCE_TWO_STEP");
+    return v != nullptr && v[0] == '1';
+  }();
+  const int two_step = (c->dev.world >= 8 || force_two_step) ? 1 : 0;
   int rc;
 #define LLMQRT_RUN(T)                                                                                              \
   rc = launch_chained(allreduce_rmsnorm_kernel<T>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,                  \
                       (cudaStream_t)stream, 1, c->dev, reinterpret_cast<const T*>(partial),                          \
                       reinterpret_cast<const T*>(x), reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), \
-                      eps, reinterpret_cast<T*>(y), q, scale_f32, H)
+                      eps, reinterpret_cast<T*>(y), q, scale_f32, H, two_step)
   if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
 #undef LLMQRT_RUN
   if (rc) return rc;

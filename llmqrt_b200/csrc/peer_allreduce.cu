@@ -68,7 +68,7 @@ int llmqrt_comm_create(int rank, int world, int64_t max_bytes, void** comm_out) 
   c->dev.world = world;
   c->dev.poll_limit_ns = kCommPollLimitNs;
   c->dev.slot_bytes = 2 * ((max_bytes + 255) / 256 * 256);            // tagged words: twice the payload
-  const size_t total = kCommCtrlBytes + (size_t)2 * kCommMaxWorld * (size_t)c->dev.slot_bytes;
+  const size_t total = kCommCtrlBytes + (size_t)2 * kCommSlots * (size_t)c->dev.slot_bytes;
   void* p = nullptr;
   cudaError_t e = cudaGetDevice(&c->device);
   if (e == cudaSuccess) e = cudaMalloc(&p, total);                     // set-up allocation; calls allocate nothing

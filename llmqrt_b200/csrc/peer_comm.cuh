@@ -2,8 +2,9 @@
 // communicator object shared by the kernels that push to and gather from them.
 //
 // Every rank owns one buffer, allocated once and mapped into every other rank's process through CUDA
-// IPC.  After a small control area it holds, per call parity p and source rank s, a slot of 16-byte
-// words
+// IPC.  After a small control area it holds, per call parity p and source rank s (plus one more
+// slot per parity for rows that arrive already reduced, see the two-step variant in glue.cu), a slot
+// of 16-byte words
 //     { data[0:4 bytes], seq, data[4:8 bytes], seq }
 // -- eight payload bytes (four 16-bit values), each half tagged with the sequence number of the call
 // that wrote it, so a word proves its own arrival and no fence, flag or barrier separates the data
@@ -23,6 +24,7 @@
 namespace llmqrt {
 
 constexpr int kCommMaxWorld = 8;
+constexpr int kCommSlots = kCommMaxWorld + 1;   // per parity: one slot per source rank + one for reduced rows
 constexpr size_t kCommCtrlBytes = 4096;                              // {sequence, status, ticket}
 constexpr unsigned long long kCommPollLimitNs = 5000000000ull;       // default bound of a poll: 5 s
 
@@ -40,7 +42,7 @@ struct Comm {                            // what the opaque handle of the C ABI 
 };
 
 __device__ __forceinline__ uint4* comm_slot(unsigned char* base, long long slot_bytes, int parity, int src) {
-  return reinterpret_cast<uint4*>(base + kCommCtrlBytes + ((size_t)parity * kCommMaxWorld + src) * (size_t)slot_bytes);
+  return reinterpret_cast<uint4*>(base + kCommCtrlBytes + ((size_t)parity * kCommSlots + src) * (size_t)slot_bytes);
 }
 __device__ __forceinline__ void comm_st_v4(uint4* p, uint4 v) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
@@ -77,6 +79,13 @@ __device__ __forceinline__ unsigned comm_enter(const CommDev& c) {
 __device__ __forceinline__ void comm_push(const CommDev& c, unsigned seq, long long word, uint2 payload) {
   const uint4 tagged = make_uint4(payload.x, seq, payload.y, seq);
   for (int p = 0; p < c.world; ++p) comm_st_v4(comm_slot(c.base[p], c.slot_bytes, (int)(seq & 1u), c.rank) + word, tagged);
+}
+
+// Stores one tagged word into slot `slot` of rank `dst` only.
+__device__ __forceinline__ void comm_push_one(const CommDev& c, unsigned seq, int dst, int slot, long long word,
+                                              uint2 payload) {
+  comm_st_v4(comm_slot(c.base[dst], c.slot_bytes, (int)(seq & 1u), slot) + word,
+             make_uint4(payload.x, seq, payload.y, seq));
 }
 
 // Polls word `word` of source rank s in the local buffer until it carries `seq`.  Returns false (and
