@@ -4,6 +4,7 @@ prompts, tensor parallel over N GPUs of one node.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --sweep [int8,fp8,awq,attn]      # one JSON line per operator shape (1 GPU)
 
 A "step" is one decode step of the whole batch (one new token per sequence).  Prints ONE JSON line
 (rank 0).  `value` is generated tokens per second with the token ids resident on the device (the step
@@ -11,6 +12,9 @@ is a replayed CUDA graph); `e2e` is the same loop driven through Qwen2Decoder.de
 pinned host buffers (ids copied to the device and sampled ids copied back every step).  `roofline`
 times the dominant kernel -- the int8 GEMM behind the four linears of every layer -- over all layers'
 weights (3.8 GB at one GPU, far larger than L2), in a CUDA graph, with CUDA events.
+Both loops are timed as BLOCKS repetitions of exactly K steps (each block restarts at the end of the
+prompt, so every block does the same work) and the median block is reported: one block of a short
+run is a few tens of milliseconds, too little to trust on its own.
 
 --impl reference times the reference's own CPU path for this workload (torch dequantize-then-matmul for
 the seven linears of a decoder layer plus a torch decode attention) on the host cores; each step is one
@@ -33,6 +37,7 @@ if ROOT not in sys.path:
 METRIC = "qwen2_7b_w8a8_decode_tokens_per_s"
 UNIT = "tokens/s"
 BATCH, PROMPT, GEN = 64, 1024, 256
+BLOCKS = 5                      # timed repetitions of the K-step region; the median is reported
 
 
 def parse_args():
@@ -45,6 +50,9 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=PROMPT)
     ap.add_argument("--layers", type=int, default=28, help="decoder layers (28 = Qwen2-7B; fewer is NOT the benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", nargs="?", const="int8,fp8,awq,attn", default=None,
+                    help="time every operator shape of the other configurations against its bound instead")
+    ap.add_argument("--reps", type=int, default=20, help="graph replays per shape of --sweep")
     return ap.parse_args()
 
 
@@ -141,7 +149,7 @@ def gemm_roofline_pass(model, batch, torch):
                     wn, sn, bn = names[nm]
                     w = getattr(L_, wn)
                     xq, xs = acts[w.shape[1]]
-                    ops.int8_linear_per_channel(xq, w, getattr(L_, bn) if bn else None, xs, getattr(L_, sn), dt)
+                    ops.int8_linear_per_channel(xq, w, getattr(L_, bn) if bn else None, xs, getattr(L_, sn), dt, True)
         body()
         torch.cuda.synchronize(dev)
         graph = torch.cuda.CUDAGraph()
@@ -269,7 +277,7 @@ def run_ours(args):
     cfg = Qwen2Config.qwen2_7b()
     cfg.num_layers = args.layers
     K, W, B = args.steps, max(args.warmup, 3), args.batch
-    max_len = args.prompt_len + W + K + 2
+    max_len = args.prompt_len + W + K + 4
     model = Qwen2Decoder(cfg, dev, batch=B, max_seq_len=max_len, tp=world, rank=rank, group=group, seed=0)
 
     def barrier():
@@ -280,52 +288,81 @@ def run_ours(args):
     prompt = torch.randint(0, cfg.vocab, (B, args.prompt_len), generator=torch.Generator().manual_seed(0)).to(dev)
     first = model.prefill(prompt).clone()
 
+    def timed_blocks(step_fn):
+        """BLOCKS x (rewind to the end of the prompt, W warm-up steps, exactly K timed steps); per block the
+        device time of the K steps, max over ranks.  Returns the list of block times in seconds."""
+        out = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(BLOCKS):
+            model.reset_position(args.prompt_len)
+            for _ in range(W):
+                step_fn()
+            barrier()
+            e0.record()
+            for _ in range(K):
+                step_fn()
+            e1.record()
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1) / 1e3], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out.append(float(t.item()))
+        return out
+
     # ---- device-resident loop -----------------------------------------------------------------
-    tok = first
+    state = {"tok": first}
     launches0 = _lib.launch_count()
-    tok = model.decode_step(tok)                      # captures the graph (one eager warm-up + capture)
+    state["tok"] = model.decode_step(state["tok"])      # captures the graph (one eager warm-up + capture)
     launches_per_step = (_lib.launch_count() - launches0) // 2
-    for _ in range(W - 1):
-        tok = model.decode_step(tok)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def dev_step():
+        state["tok"] = model.decode_step(state["tok"])
+
     with ClockSampler(local) as clocks:
-        e0.record()
-        for _ in range(K):
-            tok = model.decode_step(tok)
-        e1.record()
-        barrier()
-    elapsed = torch.tensor([e0.elapsed_time(e1) / 1e3], device=dev)
-    if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    secs = float(elapsed.item())
+        block_secs = timed_blocks(dev_step)
+    secs = statistics.median(block_secs)
 
     # ---- host-buffer loop through the public API ----------------------------------------------
-    model.reset_position(args.prompt_len)
-    h_in = first.cpu().pin_memory()
-    h_out = torch.empty_like(h_in).pin_memory()
-    for _ in range(W):
-        model.decode_step_host(h_in, h_out)
-        h_in, h_out = h_out, h_in
-    barrier()
-    e0.record()
-    for _ in range(K):
-        model.decode_step_host(h_in, h_out)
-        h_in, h_out = h_out, h_in
-    e1.record()
-    barrier()
-    elapsed = torch.tensor([e0.elapsed_time(e1) / 1e3], device=dev)
+    host = {"in": first.cpu().pin_memory()}
+    host["out"] = torch.empty_like(host["in"]).pin_memory()
+
+    def host_step():
+        model.decode_step_host(host["in"], host["out"])
+        host["in"], host["out"] = host["out"], host["in"]
+
+    block_secs_e2e = timed_blocks(host_step)
+    secs_e2e = statistics.median(block_secs_e2e)
+
+    # ---- the run is only valid if no bounded wait ran out and all ranks decoded the same tokens ----
+    problems = []
+    if _lib.kernel_status(dev) != 0:
+        problems.append("a kernel reported a bounded-wait time-out")
+    if model.comm is not None:
+        try:
+            model.comm.check()
+        except RuntimeError as e:
+            problems.append(str(e))
+    last_ids = host["in"].to(dev)                       # ids sampled by the last step, as this rank saw them
     if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    secs_e2e = float(elapsed.item())
+        ids = [torch.empty_like(last_ids) for _ in range(world)]
+        dist.all_gather(ids, last_ids)
+        if any(not torch.equal(ids[0], t) for t in ids[1:]):
+            problems.append("the ranks sampled different token ids")
+        bad = torch.tensor([1 if problems else 0], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) and not problems:
+            problems.append("another rank reported a failure")
+    if problems:
+        print(f"rank {rank}: INVALID RUN: " + "; ".join(problems), file=sys.stderr, flush=True)
+        sys.stdout.flush()
+        os._exit(3)
 
     # ---- dominant kernel --------------------------------------------------------------------------
     bytes_per_launch, secs_per_launch, gemm_shapes = gemm_roofline_pass(model, B, torch)
     attn_bytes, attn_secs = attn_roofline_pass(model, B, args.prompt_len + W + K // 2, torch)
     peak, peak_kind = measured_peak_hbm()
     achieved = bytes_per_launch / secs_per_launch / 1e9
-    status = _lib.kernel_status(dev)
-    if status != 0:
+    if _lib.kernel_status(dev) != 0:
         raise SystemExit("a kernel reported a bounded-wait time-out; the numbers are invalid")
 
     if rank == 0:
@@ -342,11 +379,17 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel<int8> (TMA + tcgen05, weights as the M operand)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
-                         # dram read + write per launch, averaged over the four linears of a layer, from the ncu
-                         # capture summarised in profiles/gemm_tc_int8_decode_ncu_full.md (1 GPU, batch 64)
-                         "traffic": 60.0e6 if (world == 1 and B == 64) else None,
+                         "traffic": 60.0e6 if (world == 1 and B == 64 and args.layers == 28) else None,
+                         "traffic_source": ("recorded constant, not measured by this run: dram__bytes_read.sum + "
+                                            "dram__bytes_write.sum per launch from one ncu capture of this kernel at this "
+                                            "configuration (1 GPU, batch 64), averaged over the four linears of a layer"
+                                            if (world == 1 and B == 64 and args.layers == 28) else None),
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": secs_per_launch * 1e6},
             "extras": {"launches_per_step": launches_per_step, "int8_gemm_by_shape": gemm_shapes,
+                       "timing": f"median of {BLOCKS} blocks of {K} steps, each block rewound to the end of the prompt",
+                       "block_ms_per_step": [t / K * 1e3 for t in block_secs],
+                       "block_ms_per_step_e2e": [t / K * 1e3 for t in block_secs_e2e],
+                       "checked": "no bounded-wait time-out; peer all-reduce status clean; identical ids on all ranks",
                        "step_hbm_gbs": step_bytes / (secs / K) / 1e9, "step_hbm_frac": step_bytes / (secs / K) / 1e9 / peak,
                        "attn_decode_gbs": attn_bytes / attn_secs / 1e9, "attn_decode_frac": attn_bytes / attn_secs / 1e9 / peak,
                        "attn_decode_us": attn_secs * 1e6},
@@ -364,9 +407,188 @@ def run_ours(args):
         os._exit(0)
 
 
+# ----------------------------------------------------------------------------------------------
+# --sweep: every operator shape of the micro-benchmark configurations against its bound
+# ----------------------------------------------------------------------------------------------
+L2_BYTES = 126 << 20
+
+
+def _time_graph(torch, body, reps):
+    """Seconds per replay of `body` captured in a CUDA graph (CUDA events around `reps` replays)."""
+    body()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / reps
+
+
+def _copies(nbytes):
+    """Distinct buffers to rotate over so that the working set exceeds L2 (at least 2, at most 64)."""
+    import math
+    return max(2, min(64, math.ceil(1.5 * L2_BYTES / max(nbytes, 1))))
+
+
+def measure_pipe_peaks(torch):
+    """Dense tensor-pipe rates of this GPU measured the way MEASURED_PEAKS.json measures bf16: the
+    library GEMM at 8192^3, best of 10.  Used only as roofline denominators of the sweep."""
+    dev = torch.device("cuda")
+    n = 8192
+    out = {}
+
+    def best(fn):
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 1e3)
+        return 2 * n ** 3 / min(ts)
+
+    a16 = torch.randn(n, n, device=dev, dtype=torch.bfloat16)
+    b16 = torch.randn(n, n, device=dev, dtype=torch.bfloat16)
+    out["bf16"] = best(lambda: torch.matmul(a16, b16.t()))
+    try:
+        a8, b8 = a16.to(torch.float8_e4m3fn), b16.to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev)
+        out["fp8"] = best(lambda: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+    except Exception:
+        out["fp8"] = None
+    try:
+        ai = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+        bi = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+        out["int8"] = best(lambda: torch._int_mm(ai, bi.t()))
+    except Exception:
+        out["int8"] = None
+    return out
+
+
+def run_sweep(args):
+    """One JSON line per operator shape: time, algorithmic GB/s and TOP/s, bound = max(bytes / HBM,
+    flops / pipe), frac = bound / time.  Every shape is replayed from a CUDA graph that rotates over
+    enough distinct weight (or KV) buffers to exceed L2."""
+    import torch
+    from llmqrt_b200 import _lib, ops
+    from llmqrt_b200.attention import attn_decode, flash_attn_func
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --sweep needs a CUDA device")
+    dev = torch.device("cuda")
+    hbm_gbs, peak_kind = measured_peak_hbm()
+    hbm = hbm_gbs * 1e9
+    pipes = measure_pipe_peaks(torch)
+    pipe16 = pipes["bf16"]
+    pipe_f8 = pipes["fp8"] or 2 * pipe16
+    pipe_i8 = pipes["int8"] or 2 * pipe16
+    print(json.dumps({"sweep": "peaks", "hbm_gbs": hbm_gbs, "hbm_source": peak_kind,
+                      "pipe_tflops_measured_here": {k: (v / 1e12 if v else None) for k, v in pipes.items()},
+                      "note": "pipes = library GEMM at 8192^3, best of 10; a kind the library refuses falls back "
+                              "to twice the bf16 figure"}), flush=True)
+    reps = args.reps
+
+    def report(tag, M, N, K, secs, nbytes, flops, pipe, **extra):
+        bound = max(nbytes / hbm, flops / pipe)
+        print(json.dumps({"sweep": tag, "M": M, "N": N, "K": K, "us": secs * 1e6, "gbs": nbytes / secs / 1e9,
+                          "tops": flops / secs / 1e12, "bound_us": bound * 1e6,
+                          "bound": "hbm" if nbytes / hbm >= flops / pipe else "pipe", "frac": bound / secs, **extra}),
+              flush=True)
+
+    what = args.sweep.split(",")
+    if "int8" in what:
+        g = torch.Generator(device=dev).manual_seed(0)
+        shapes = [("sq qwen2-0.5b gate", 16, 4864, 896)]
+        for M in (64, 4096):
+            shapes += [("sq 7b qkv", M, 4608, 3584), ("sq 7b o", M, 3584, 3584), ("sq 7b gate_up", M, 37888, 3584),
+                       ("sq 7b down", M, 3584, 18944)]
+        for tag, M, N, K in shapes:
+            n = _copies(N * K)
+            ws = [torch.randint(-127, 128, (N, K), generator=g, device=dev, dtype=torch.int8) for _ in range(n)]
+            a = torch.randint(-127, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+            sa = torch.rand(M, generator=g, device=dev) * 1e-2
+            sw = torch.rand(N, generator=g, device=dev) * 1e-2
+            secs = _time_graph(torch, lambda: [ops.int8_linear_per_channel(a, w, None, sa, sw, torch.bfloat16, True)
+                                               for w in ws], reps) / n
+            report(tag, M, N, K, secs, gemm_bytes(M, N, K, False), 2 * M * N * K, pipe_i8)
+            if M == 16:                                  # the allocation-free entry point on the same shape
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+                def noalloc():
+                    for w in ws:
+                        _lib.call("llmqrt_w8a8_int8_linear_per_channel_noalloc", _lib.ptr(a), a.stride(0), _lib.ptr(w),
+                                  w.stride(0), None, _lib.F16, _lib.ptr(sa), _lib.ptr(sw), _lib.ptr(out), _lib.BF16, N,
+                                  M, N, K, _lib.stream(dev))
+                noalloc()                                # resolves the scratch address before any capture
+                secs = _time_graph(torch, noalloc, reps) / n
+                report(tag + " (no-alloc entry)", M, N, K, secs, gemm_bytes(M, N, K, False), 2 * M * N * K, pipe_i8)
+            del ws
+    if "fp8" in what:
+        g = torch.Generator(device=dev).manual_seed(1)
+        for tag, N, K in (("fp8 q/o", 896, 896), ("fp8 k/v", 128, 896), ("fp8 gate/up", 4864, 896), ("fp8 down", 896, 4864)):
+            for M in (1, 16, 64, 1024, 4096):
+                n = _copies(N * K)
+                ws = [(torch.randn(N, K, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn) for _ in range(n)]
+                a = torch.randn(M, K, generator=g, device=dev).to(torch.float8_e4m3fn)
+                sa = torch.rand(M, 1, generator=g, device=dev) * 1e-2
+                sw = torch.rand(1, N, generator=g, device=dev) * 1e-2
+                secs = _time_graph(torch, lambda: [ops.fp8_linear_rowwise(a, w, None, sa, sw, True) for w in ws], reps) / n
+                report(tag, M, N, K, secs, gemm_bytes(M, N, K, False), 2 * M * N * K, pipe_f8)
+    if "awq" in what:
+        g = torch.Generator(device=dev).manual_seed(2)
+        G = 128
+        for tag, N, K in (("awq qkv", 2048, 1536), ("awq o", 1536, 1536), ("awq gate", 8960, 1536),
+                          ("awq gate_up", 17920, 1536), ("awq down", 1536, 8960)):
+            for M in (1, 16, 256, 2048):
+                wbytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2
+                n = _copies(wbytes)
+                layers = []
+                for _ in range(n):                       # nibbles uniform, scales ~ U(0.001, 0.02)
+                    qweight = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), generator=g, device=dev, dtype=torch.int32)
+                    qzeros = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // G, N // 8), generator=g, device=dev, dtype=torch.int32)
+                    scales = (torch.rand(K // G, N, generator=g, device=dev) * 0.019 + 0.001).half()
+                    layers.append(ops.AwqPacked(qweight, scales, qzeros))
+                x = torch.randn(M, K, generator=g, device=dev).half()
+                secs = _time_graph(torch, lambda: [ops.awq_gemm(x, p) for p in layers], reps) / n
+                report(tag, M, N, K, secs, 2 * M * K + wbytes + 2 * M * N, 2 * M * N * K, pipe16)
+    if "attn" in what:
+        g = torch.Generator(device=dev).manual_seed(3)
+        B, Hq, Hkv, d, Smax = 32, 28, 4, 128, 8192
+        lens = torch.randint(512, 8193, (B,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+        kc = torch.randn(B, Smax, Hkv, d, generator=g, device=dev, dtype=torch.float16)     # 268 MB each: beyond L2
+        vc = torch.randn(B, Smax, Hkv, d, generator=g, device=dev, dtype=torch.float16)
+        q = torch.randn(B, Hq, d, generator=g, device=dev, dtype=torch.float16)
+        ld = lens.to(dev)
+        secs = _time_graph(torch, lambda: attn_decode(q, kc, vc, ld, Smax), reps)
+        ctx = int(lens.sum())
+        report("attn decode b32 ctx U[512,8192]", B, ctx // B, d, secs, ctx * Hkv * d * 2 * 2 + 2 * B * Hq * d * 2,
+               4 * ctx * Hq * d, pipe16)
+        del kc, vc
+        Bp, S = 4, 2048
+        qs = [torch.randn(Bp, S, Hq, d, generator=g, device=dev, dtype=torch.float16) for _ in range(2)]
+        ks = [torch.randn(Bp, S, Hkv, d, generator=g, device=dev, dtype=torch.float16) for _ in range(2)]
+        vs = [torch.randn(Bp, S, Hkv, d, generator=g, device=dev, dtype=torch.float16) for _ in range(2)]
+        secs = _time_graph(torch, lambda: [flash_attn_func(a, b, c, causal=True) for a, b, c in zip(qs, ks, vs)], reps) / 2
+        report("attn prefill 4x2048 causal", Bp * S, S, d, secs, Bp * S * (2 * Hq + 2 * Hkv) * d * 2,
+               4 * Bp * Hq * S * S * d // 2, pipe16)
+    if _lib.kernel_status(dev) != 0:
+        raise SystemExit("a kernel reported a bounded-wait time-out; the sweep is invalid")
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.sweep is not None:
+        run_sweep(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

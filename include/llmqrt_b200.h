@@ -88,11 +88,14 @@ int llmqrt_quantize_fp8_static(const void* x, int x_dtype, int64_t M, int64_t K,
  * W8A8 GEMMs.   acc[m, n] = sum_k a[m, k] * w[n, k]
  * Requirements: K % 16 == 0, lda % 16 == 0, ldw % 16 == 0, 16-byte aligned a and w.
  * `alpha_dev`, when not NULL, is a device fp32 scalar used instead of `alpha`.
- * `w` is a stored weight: the kernels may start reading it before the kernel that precedes the
- * call on `stream` has finished (they only wait for that kernel before touching `a`, the scales
- * and `out`), so `w` must not be produced by that preceding kernel.  llmqrt_gemm_16bit makes no
- * such assumption.
+ * `flags`: 0, or LLMQRT_GEMM_STATIC_WEIGHT when `w` is a stored weight that no kernel still
+ * running or queued on `stream` writes.  With that flag the kernels may start reading `w` before
+ * the kernel that precedes the call on `stream` has finished (they still wait for it before
+ * touching `a`, the scales and `out`), which hides the first weight fetch behind the previous
+ * kernel's tail.  Without it every operand is read only after the preceding kernel has completed,
+ * so a weight quantized on the same stream right before the call is safe.
  * ---------------------------------------------------------------------------------------- */
+enum { LLMQRT_GEMM_STATIC_WEIGHT = 1 };
 
 /* int8 x int8 -> exact int32 accumulators -> out fp16 = alpha * acc + beta * bias[n].
  * bias is fp16 [N] and required, like the reference's.
@@ -100,7 +103,7 @@ int llmqrt_quantize_fp8_static(const void* x, int x_dtype, int64_t M, int64_t K,
  *      declared runtime/csrc/smoothquant/sq_gemm.h:12-17, bound runtime/csrc/bindings.cpp:10-11. */
 int llmqrt_w8a8_int8_linear_per_tensor(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, const void* bias,
                                        float alpha, const float* alpha_dev, float beta, void* out, int64_t ldo,
-                                       int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+                                       int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags);
 
 /* int8 GEMM with the per-token x per-output-channel dequantization fused:
  * out = T( (float(acc) * w_scale[n]) * a_scale[m] + bias[n] ), T = out_dtype, bias optional.
@@ -110,7 +113,7 @@ int llmqrt_w8a8_int8_linear_per_tensor(const int8_t* a, int64_t lda, const int8_
 int llmqrt_w8a8_int8_linear_per_channel(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, const void* bias,
                                         int bias_dtype, const float* a_scale, const float* w_scale, void* out,
                                         int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
-                                        llmqrt_stream_t stream);
+                                        llmqrt_stream_t stream, int flags);
 
 /* Same operator as llmqrt_w8a8_int8_linear_per_channel for callers that cannot hand over a workspace
  * because they are not allowed, or cannot afford, to allocate device memory: plug-ins of a server
@@ -130,7 +133,7 @@ int llmqrt_w8a8_int8_linear_per_channel_noalloc(const int8_t* a, int64_t lda, co
 /* Raw int32 accumulators acc[M, ldo] of the int8 GEMM (the quantity the parity gate checks bit for
  * bit); same kernels as the two entry points above with the epilogue reduced to a store. */
 int llmqrt_w8a8_int8_gemm_s32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldo,
-                              int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+                              int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags);
 
 /* FP8 GEMM, tensor-wise scaling: out = T( alpha * acc_f32 + beta * bias[n] ), T in {bf16, fp16},
  * bias optional and of type T.  a_format = LLMQRT_E4M3 or LLMQRT_E5M2; w is e4m3.
@@ -138,7 +141,7 @@ int llmqrt_w8a8_int8_gemm_s32(const int8_t* a, int64_t lda, const int8_t* w, int
  *      runtime/csrc/fp8/sm89_fp8_tensorwise_cutlassgemm.cu:316-334, bindings.cpp:12. */
 int llmqrt_f8f8_tensorwise(const uint8_t* a, int a_format, int64_t lda, const uint8_t* w, int64_t ldw,
                            const void* bias, float alpha, const float* alpha_dev, float beta, void* out, int out_dtype,
-                           int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+                           int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags);
 
 /* FP8 GEMM, row-wise scaling: out bf16 = ((acc_f32 * x_scale[m]) * w_scale[n]) + bias[n];
  * bias optional, bf16 or fp32.
@@ -146,7 +149,7 @@ int llmqrt_f8f8_tensorwise(const uint8_t* a, int a_format, int64_t lda, const ui
  *      runtime/csrc/fp8/sm89_fp8_rowwise_fbgemm.cu:582-606, bindings.cpp:13. */
 int llmqrt_f8f8bf16_rowwise(const uint8_t* a, int a_format, int64_t lda, const uint8_t* w, int64_t ldw,
                             const void* bias, int bias_dtype, const float* x_scale, const float* w_scale, void* out,
-                            int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream);
+                            int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags);
 
 /* Path selection of the W8A8 GEMMs, for tests and benchmarks: 0 = automatic (default),
  * 1 = register-operand streaming kernel only, 2 = tcgen05/TMEM kernel only.  Process-wide. */
@@ -211,6 +214,10 @@ int llmqrt_kv_append(void* k_cache, void* v_cache, int64_t cache_batch_stride, i
  * out_q / out_scale (both or neither; may be NULL): additionally the per-token int8 quantization of
  * out viewed as [B, Hq * d] -- the same arithmetic as llmqrt_quantize_int8(per_token = 1) applied to
  * out, scales as fp32 -- which is the input of an int8 output projection (Hq * d <= 8192).
+ * max_seqlen: upper bound of seqlens[b], at most the cache capacity; the grid and the split-KV
+ * scratch are sized from it without reading seqlens back.  A sequence whose length exceeds it is
+ * attended over its first max_seqlen rows only (and llmqrt_attn_decode_append writes nothing for
+ * it): no access outside the cache or the scratch results.
  * ref: flash_attn_with_kvcache call site, runtime/nn_models/modules/nonlinear/attn.py:300-315;
  *      the quantization that follows it in an int8 model: quantize_activation_per_token_absmax,
  *      runtime/nn_models/modules/linear/linear_sq.py:56-65, called from

@@ -39,12 +39,12 @@ _PROTOS = {
     "llmqrt_quantize_int8": (c_int, [P, I32, I64, I64, I64, I32, P, P, P, F, P, P]),
     "llmqrt_quantize_fp8": (c_int, [P, I32, I64, I64, I64, I32, P, P, F, P, P]),
     "llmqrt_quantize_fp8_static": (c_int, [P, I32, I64, I64, I64, P, P, P]),
-    "llmqrt_w8a8_int8_linear_per_tensor": (c_int, [P, I64, P, I64, P, F, P, F, P, I64, I64, I64, I64, P, P]),
-    "llmqrt_w8a8_int8_linear_per_channel": (c_int, [P, I64, P, I64, P, I32, P, P, P, I32, I64, I64, I64, I64, P, P]),
+    "llmqrt_w8a8_int8_linear_per_tensor": (c_int, [P, I64, P, I64, P, F, P, F, P, I64, I64, I64, I64, P, P, I32]),
+    "llmqrt_w8a8_int8_linear_per_channel": (c_int, [P, I64, P, I64, P, I32, P, P, P, I32, I64, I64, I64, I64, P, P, I32]),
     "llmqrt_w8a8_int8_linear_per_channel_noalloc": (c_int, [P, I64, P, I64, P, I32, P, P, P, I32, I64, I64, I64, I64, P]),
-    "llmqrt_w8a8_int8_gemm_s32": (c_int, [P, I64, P, I64, P, I64, I64, I64, I64, P, P]),
-    "llmqrt_f8f8_tensorwise": (c_int, [P, I32, I64, P, I64, P, F, P, F, P, I32, I64, I64, I64, I64, P, P]),
-    "llmqrt_f8f8bf16_rowwise": (c_int, [P, I32, I64, P, I64, P, I32, P, P, P, I64, I64, I64, I64, P, P]),
+    "llmqrt_w8a8_int8_gemm_s32": (c_int, [P, I64, P, I64, P, I64, I64, I64, I64, P, P, I32]),
+    "llmqrt_f8f8_tensorwise": (c_int, [P, I32, I64, P, I64, P, F, P, F, P, I32, I64, I64, I64, I64, P, P, I32]),
+    "llmqrt_f8f8bf16_rowwise": (c_int, [P, I32, I64, P, I64, P, I32, P, P, P, I64, I64, I64, I64, P, P, I32]),
     "llmqrt_awq_dequantize": (c_int, [P, P, P, I64, I64, I64, P, P]),
     "llmqrt_awq_repack": (c_int, [P, P, P, I64, I64, I64, P, P, P]),
     "llmqrt_awq_gemm": (c_int, [P, I64, P, P, P, P, I64, I64, I64, I64, I64, P, P]),
@@ -86,7 +86,7 @@ def _bind(lib: ctypes.CDLL) -> list[str]:
     return missing
 
 
-ABI_VERSION = 3          # llmqrt_abi_version() of the sources these prototypes describe
+ABI_VERSION = 4          # llmqrt_abi_version() of the sources these prototypes describe
 
 _missing = _bind(_lib)
 if not _missing and _lib.llmqrt_abi_version() != ABI_VERSION:
@@ -182,6 +182,9 @@ def kernel_status(device: torch.device) -> int:
 def launch_count() -> int:
     """Kernels launched by the library so far in this process."""
     return int(_lib.llmqrt_launch_count())
+
+
+GEMM_STATIC_WEIGHT = 1   # LLMQRT_GEMM_STATIC_WEIGHT of the header
 
 
 def set_gemm_path(path: int) -> None:

@@ -146,8 +146,8 @@ __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const uint16_t* __restrict__ k_cache,
                    const uint16_t* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
                    const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int Hkv, int chunk,
-                   int max_splits, float scale, float softcap, float* __restrict__ part_o, float* __restrict__ part_ml,
-                   DecodeAppend ap) {
+                   int max_splits, int max_len, float scale, float softcap, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, DecodeAppend ap) {
   constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
   constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
   LLMQRT_TIMELINE_MARK(40);
@@ -156,7 +156,11 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
   LLMQRT_TIMELINE_MARK(41);
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int rep = Hq / Hkv;
-  const int L = seqlens[b];
+  // A length beyond the bound the grid and the partial slots were sized for (the host's max_seqlen,
+  // at most the cache capacity) is clamped: the sequence is attended over its first max_len rows and
+  // nothing is appended, so neither the cache nor a neighbour's partial slots are touched.
+  const int L_raw = seqlens[b];
+  const int L = min(L_raw, max_len);
   const int key_begin = split * chunk;
   if (key_begin >= L && !(L == 0 && split == 0)) return;
   const int key_end = min(L, key_begin + chunk);
@@ -202,7 +206,8 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
   }
   // (block-uniform condition; like the stand-alone rotary kernel, a position outside the table
   // leaves the cache untouched)
-  if (ap.k_new != nullptr && pos >= key_begin && pos < key_end && (ap.cos_tab == nullptr || rotate)) {
+  if (ap.k_new != nullptr && L_raw <= max_len && pos >= key_begin && pos < key_end &&
+      (ap.cos_tab == nullptr || rotate)) {
     const int64_t src = (int64_t)b * ap.kv_batch_stride + (int64_t)hkv * D;
     const int64_t dst = (int64_t)b * cache_batch_stride + (int64_t)pos * cache_row_stride + (int64_t)hkv * D;
     uint16_t* kc = const_cast<uint16_t*>(k_cache);
@@ -413,7 +418,8 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
 template <bool BF16, int D>
 __global__ void __launch_bounds__(1024)
 attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int chunk,
-                           int max_splits, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                           int max_splits, int max_len, const float* __restrict__ part_o,
+                           const float* __restrict__ part_ml,
                            int8_t* __restrict__ out_q, float* __restrict__ out_scale) {
   extern __shared__ __align__(16) uint8_t row_raw[];
   __shared__ float red[32];
@@ -421,7 +427,7 @@ attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __rest
   pdl_trigger_then_wait();
   LLMQRT_TIMELINE_MARK(51);
   const int b = blockIdx.x;
-  const int L = seqlens[b];
+  const int L = min(seqlens[b], max_len);          // same clamp as the main kernel
   const int n_splits = (L + chunk - 1) / chunk;
   if (n_splits <= 1 && !out_q) return;             // the main kernel already wrote the result
   merge_sequence<BF16, D>(b, n_splits, out, Hq, max_splits, part_o, part_ml, out_q, out_scale,
@@ -484,7 +490,7 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
                               reinterpret_cast<const uint16_t*>(q), qbs, reinterpret_cast<const uint16_t*>(kc),
                               reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
-                              Hq, Hkv, chunk, max_splits, scale, softcap, part_o, part_ml, ap))
+                              Hq, Hkv, chunk, max_splits, max_seqlen, scale, softcap, part_o, part_ml, ap))
     return rc;
   if (int rc = check_launch("attn_decode")) return rc;
   if (need_merge) {
@@ -492,7 +498,7 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
     const int threads = units >= 1024 ? 1024 : (units + 31) / 32 * 32;
     const size_t row_smem = out_q ? (size_t)Hq * D * 2 : 0;
     if (int rc = launch_chained(attn_decode_combine_kernel<BF16, D>, dim3(B), dim3(threads), row_smem, st, 1, seqlens,
-                                reinterpret_cast<uint16_t*>(out), Hq, chunk, max_splits,
+                                reinterpret_cast<uint16_t*>(out), Hq, chunk, max_splits, max_seqlen,
                                 static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out_q,
                                 out_scale))
       return rc;

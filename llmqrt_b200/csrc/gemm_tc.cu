@@ -17,8 +17,9 @@
 // epilogue; peers are released by remote mbarrier arrivals instead of a second cluster barrier.  No
 // global scratch, no atomics, no second kernel.
 //
-// Launched with programmatic dependent launch: the block's first ring of WEIGHT tiles is requested
-// before griddepcontrol.wait (weights are constants of the model), the activation tiles after it.
+// Launched with programmatic dependent launch: when the caller declares the weights static (constants
+// of the model), the block's first ring of WEIGHT tiles is requested before griddepcontrol.wait and
+// only the activation tiles after it; otherwise every tile waits.
 //
 // Warp roles (192 threads): warp 0 lane 0 issues TMA; warp 1 owns tensor memory and its lane 0
 // issues the MMAs; warps 2-5 run the epilogue (TMEM lane quadrant = warp id % 4).  All waits on
@@ -52,6 +53,7 @@ struct TcParams {
   int k_blocks;                    // ceil(K bytes / 128)
   int tiles_p, tiles_q, splits;    // splits == cluster size along K (1, 2, 4 or 8)
   int swap;                        // 0: P = tokens (i -> m, j -> n); 1: P = weights (i -> n, j -> m)
+  int early_w;                     // weight tiles of the first ring may be requested before the dependency wait
   int M, N;
   uint32_t idesc;
   unsigned* status;                // set to 1 if a bounded wait ran out
@@ -332,6 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __shared__ __align__(16) float q_bias[BN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int cluster_abort;                        // split mode: set in every CTA of the cluster by one that failed
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort = &abort_flag;
@@ -351,6 +354,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     TC_TRACE(11);
     TC_TRACE(0);
     abort_flag = 0;
+    cluster_abort = 0;
     for (int s = 0; s < kStages; ++s) {
       tc::mbar_init(tc::smem_u32(&bar_full[s]), 1);
       tc::mbar_init(tc::smem_u32(&bar_empty[s]), 1);
@@ -406,11 +410,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       // first work item is requested BEFORE waiting for the preceding kernel of the stream; the
       // activation tiles of the same stages follow after the wait and complete the same barriers.
       // On a programmatic launch this streams up to a ring of weights per SM while the preceding
-      // kernel is still running.  Only for the 8-bit kinds, whose W is by contract a stored weight:
-      // the 16-bit GEMM is also handed matrices that the preceding kernel has just produced (an AWQ
-      // layer dequantized for a large M), so it waits first.
-      constexpr bool kEarlyWeights = KIND != tc::MMA_F16;
-      if (!kEarlyWeights) {
+      // kernel is still running.  Only when the caller declared W a stored weight: a matrix that the
+      // preceding kernel has just produced (a weight quantized on the fly, an AWQ layer dequantized
+      // for a large M) must be waited for like the activations.
+      const bool early_w = prm.early_w != 0;
+      if (!early_w) {
         pdl_wait();
         TC_TRACE(12);
         pdl_trigger();
@@ -430,7 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           if (load_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
           else tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
         }
-        if (phase_w && kEarlyWeights) {
+        if (phase_w && early_w) {
           // (Prefetching further weight tiles into L2 here was measured to slow the kernel down: the
           // ring already keeps more bytes in flight than HBM needs, and the activation loads then
           // queue behind the prefetches.)
@@ -584,11 +588,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     const int cpo = BN / S;                            // accumulator columns owned by each CTA
     const uint32_t slice_bytes = (uint32_t)cpo * kBM * 4;
     uint32_t* send = reinterpret_cast<uint32_t*>(tiles + BN * kBM * 4);
-    const bool healthy = abort_flag == 0;              // own MMAs finished (epilogue warps waited for them)
+    const bool own_healthy = abort_flag == 0;          // own MMAs finished (epilogue warps waited for them)
     const int quad = warp & 3, et = quad * 32 + lane;
     const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
     const EpiConsts& ec = ec_split;                    // q_scale / q_bias cover only the columns this CTA owns
-    if (warp >= 2 && healthy) {
+    if (warp >= 2 && own_healthy) {
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
       // 32 columns per round trip to tensor memory (four loads in flight before the wait): the
       // wait, not the data volume, is what each round costs
@@ -607,9 +611,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       if (threadIdx.x == 64) TC_TRACE(7);
       if (threadIdx.x == 64) tc::mbar_arrive_expect_tx(tc::smem_u32(&bar_reduce), slice_bytes * (uint32_t)S);
     }
-    // Cluster barrier: every ring is dead, every `send` is complete, every `bar_reduce` is armed.
+    // A CTA whose waits ran out tells every CTA of the cluster before the barrier, and then ALL of
+    // them skip the exchange: nobody copies into, or arrives on a barrier of, a CTA that may have left.
+    if (!own_healthy && threadIdx.x == 64) {
+      for (int o = 0; o < S; ++o) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(tc::smem_u32(&cluster_abort)), "r"(o));
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(1u) : "memory");
+      }
+    }
+    // Cluster barrier: every ring is dead, every `send` is complete, every `bar_reduce` is armed,
+    // every failure flag has landed (release / acquire).
     __syncwarp();
     cluster_sync_all();
+    const bool healthy = own_healthy && *reinterpret_cast<volatile int*>(&cluster_abort) == 0;
+    if (!healthy && threadIdx.x == 64) abort_flag = 1;                 // reported through the status word at exit
     if (threadIdx.x == 64 && healthy) {
       for (int o = 0; o < S; ++o)
         bulk_copy_to_cta(tc::smem_u32(tiles) + (uint32_t)my_split * slice_bytes,
@@ -812,7 +828,7 @@ int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const Tc
 }  // namespace
 
 int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
-            const Epilogue& epi, void* workspace, cudaStream_t st) {
+            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w) {
   const int elt = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
   LLMQRT_REQUIRE((K * elt) % 16 == 0 && (lda * elt) % 16 == 0 && (ldw * elt) % 16 == 0,
                  "tcgen05 gemm: K and leading dimensions must cover multiples of 16 bytes");
@@ -820,30 +836,23 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
                  "tcgen05 gemm: operands must be 16-byte aligned");
 
   // A mid-sized M with a narrow N has only a handful of 128 x 256 tiles, and that schedule has no
-  // split-K: most SMs would idle (M = 256, N = 1536, K = 8960: 12 tiles, 76 us; as panels 42 us).  Such problems run as
-  // panels of 128 rows through the small-M schedule, whose cluster split-K fills the machine; the
-  // weights of the second and later panels come from L2.
+  // split-K: most SMs would idle (M = 256, N = 1536, K = 8960: 12 tiles).  Such problems run through
+  // the small-M schedule instead -- weights as the 128-lane operand, tokens in panels of 128 as the
+  // column operand, cluster split-K -- as ONE launch whose grid covers every (weight tile, token
+  // panel) pair; neighbouring clusters share a weight tile, so the panels after the first read it
+  // from L2.
+  bool panels = false;
   if (M > 128 && M <= 1024) {
     const int64_t tiles = ceil_div(M, (int64_t)kBM) * ceil_div(N, (int64_t)(N <= 128 ? 128 : 256));
-    if (tiles * 4 <= sm_count()) {
-      const int64_t out_es = epi.mode == EPI_RAW ? 4 : 2;
-      for (int64_t m0 = 0; m0 < M; m0 += kBM) {
-        Epilogue e = epi;
-        e.out = static_cast<char*>(epi.out) + m0 * epi.ldo * out_es;
-        if (e.row_scale) e.row_scale += m0;
-        const int64_t rows = M - m0 < kBM ? M - m0 : kBM;
-        if (int rc = gemm_tc(kind, static_cast<const char*>(A) + m0 * lda * elt, lda, W, ldw, rows, N, K, e, workspace, st))
-          return rc;
-      }
-      return LLMQRT_OK;
-    }
+    panels = tiles * 4 <= sm_count();
   }
 
   TcParams prm{};
   prm.M = (int)M;
   prm.N = (int)N;
   prm.epi = epi;
-  prm.swap = M <= 128 ? 1 : 0;
+  prm.early_w = static_w ? 1 : 0;
+  prm.swap = (M <= 128 || panels) ? 1 : 0;
   int bn;
   if (prm.swap) bn = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
   else bn = N <= 128 ? 128 : 256;

@@ -28,14 +28,15 @@ int check_common(const void* a, int64_t lda, const void* w, int64_t ldw, const v
 }
 
 int run(int kind, const void* a, int64_t lda, const void* w, int64_t ldw, int64_t M, int64_t N, int64_t K,
-        const Epilogue& epi, void* workspace, cudaStream_t st) {
+        const Epilogue& epi, void* workspace, cudaStream_t st, int flags) {
   if (M == 0) return LLMQRT_OK;
+  LLMQRT_REQUIRE((flags & ~LLMQRT_GEMM_STATIC_WEIGHT) == 0, "w8a8 gemm: unknown flags 0x%x", flags);
   const int path = g_path.load();
   const bool stream = path == 1 || (path == 0 && M <= kStreamMaxM);
   if (stream)
     return w8a8_gemm_stream(kind, reinterpret_cast<const uint8_t*>(a), lda, reinterpret_cast<const uint8_t*>(w), ldw,
                             M, N, K, epi, workspace, st);
-  return gemm_tc(kind, a, lda, w, ldw, M, N, K, epi, workspace, st);
+  return gemm_tc(kind, a, lda, w, ldw, M, N, K, epi, workspace, st, (flags & LLMQRT_GEMM_STATIC_WEIGHT) != 0);
 }
 
 int f8_kind(int a_format) {
@@ -62,19 +63,19 @@ int llmqrt_set_gemm_path(int path) {
 
 int llmqrt_w8a8_int8_linear_per_tensor(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, const void* bias,
                                        float alpha, const float* alpha_dev, float beta, void* out, int64_t ldo,
-                                       int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream) {
+                                       int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags) {
   if (int rc = check_common(a, lda, w, ldw, out, ldo, M, N, K)) return rc;
   LLMQRT_REQUIRE(bias, "int8 per-tensor linear: bias is required (pass zeros for none)");
   Epilogue e{};
   e.mode = EPI_TENSOR; e.out_dtype = LLMQRT_F16; e.bias_dtype = LLMQRT_F16; e.alpha = alpha; e.beta = beta;
   e.alpha_dev = alpha_dev; e.bias = bias; e.out = out; e.ldo = ldo;
-  return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream);
+  return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream, flags);
 }
 
 int llmqrt_w8a8_int8_linear_per_channel(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, const void* bias,
                                         int bias_dtype, const float* a_scale, const float* w_scale, void* out,
                                         int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
-                                        llmqrt_stream_t stream) {
+                                        llmqrt_stream_t stream, int flags) {
   if (int rc = check_common(a, lda, w, ldw, out, ldo, M, N, K)) return rc;
   LLMQRT_REQUIRE(a_scale && w_scale, "int8 per-channel linear: null scale");
   LLMQRT_REQUIRE(out_dtype == LLMQRT_F16 || out_dtype == LLMQRT_BF16, "int8 per-channel linear: out must be fp16/bf16");
@@ -83,20 +84,20 @@ int llmqrt_w8a8_int8_linear_per_channel(const int8_t* a, int64_t lda, const int8
   Epilogue e{};
   e.mode = EPI_COL_ROW; e.out_dtype = out_dtype; e.bias_dtype = bias_dtype; e.bias = bias; e.row_scale = a_scale;
   e.col_scale = w_scale; e.out = out; e.ldo = ldo;
-  return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream);
+  return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream, flags);
 }
 
 int llmqrt_w8a8_int8_gemm_s32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldo,
-                              int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream) {
+                              int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags) {
   if (int rc = check_common(a, lda, w, ldw, acc, ldo, M, N, K)) return rc;
   Epilogue e{};
   e.mode = EPI_RAW; e.out_dtype = LLMQRT_F32; e.out = acc; e.ldo = ldo;
-  return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream);
+  return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream, flags);
 }
 
 int llmqrt_f8f8_tensorwise(const uint8_t* a, int a_format, int64_t lda, const uint8_t* w, int64_t ldw,
                            const void* bias, float alpha, const float* alpha_dev, float beta, void* out, int out_dtype,
-                           int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream) {
+                           int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags) {
   if (int rc = check_common(a, lda, w, ldw, out, ldo, M, N, K)) return rc;
   const int kind = f8_kind(a_format);
   LLMQRT_REQUIRE(kind >= 0, "fp8 tensorwise: activations must be e4m3 or e5m2");
@@ -104,12 +105,12 @@ int llmqrt_f8f8_tensorwise(const uint8_t* a, int a_format, int64_t lda, const ui
   Epilogue e{};
   e.mode = EPI_TENSOR; e.out_dtype = out_dtype; e.bias_dtype = out_dtype; e.alpha = alpha; e.beta = beta;
   e.alpha_dev = alpha_dev; e.bias = bias; e.out = out; e.ldo = ldo;
-  return run(kind, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream);
+  return run(kind, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream, flags);
 }
 
 int llmqrt_f8f8bf16_rowwise(const uint8_t* a, int a_format, int64_t lda, const uint8_t* w, int64_t ldw,
                             const void* bias, int bias_dtype, const float* x_scale, const float* w_scale, void* out,
-                            int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream) {
+                            int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags) {
   if (int rc = check_common(a, lda, w, ldw, out, ldo, M, N, K)) return rc;
   const int kind = f8_kind(a_format);
   LLMQRT_REQUIRE(kind >= 0, "fp8 rowwise: activations must be e4m3 or e5m2");
@@ -118,7 +119,7 @@ int llmqrt_f8f8bf16_rowwise(const uint8_t* a, int a_format, int64_t lda, const u
   Epilogue e{};
   e.mode = EPI_ROW_COL; e.out_dtype = LLMQRT_BF16; e.bias_dtype = bias_dtype; e.bias = bias; e.row_scale = x_scale;
   e.col_scale = w_scale; e.out = out; e.ldo = ldo;
-  return run(kind, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream);
+  return run(kind, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream, flags);
 }
 
 }  // extern "C"

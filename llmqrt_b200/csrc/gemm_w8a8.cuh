@@ -16,9 +16,11 @@ enum GemmKind : int {
 int w8a8_gemm_stream(int kind, const uint8_t* A, int64_t lda, const uint8_t* W, int64_t ldw, int64_t M, int64_t N,
                      int64_t K, const Epilogue& epi, void* workspace, cudaStream_t st);
 
-// TMA + tcgen05/TMEM kernel (gemm_tc.cu): any M; lda/ldw in elements.
+// TMA + tcgen05/TMEM kernel (gemm_tc.cu): any M; lda/ldw in elements.  static_w: W is a stored weight
+// that nothing queued on the stream writes, so its first tiles may be requested before the
+// preceding kernel of the stream has completed.
 int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
-            const Epilogue& epi, void* workspace, cudaStream_t st);
+            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w = false);
 
 // Path selection shared by all entry points (0 auto, 1 streaming, 2 tcgen05).
 int gemm_path();

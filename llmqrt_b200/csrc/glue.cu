@@ -344,8 +344,10 @@ rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* 
 // `partial` to all ranks through the peer-mapped buffers, gathers the W copies, adds them in rank
 // order in fp32 and rounds to T -- exactly the stand-alone all-reduce -- and goes on with
 // h = x + that sum.  One kernel instead of all-reduce + RMSNorm.
-template <typename T>
-__global__ void __launch_bounds__(1024)
+// MAXT bounds the block size (512 leaves 128 registers per thread: the gathered copies of eight
+// ranks stay in registers).
+template <typename T, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __restrict__ x, T* __restrict__ x_out,
                          const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
                          float* __restrict__ scale_f32, int64_t H, int two_step) {
@@ -353,22 +355,36 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
   pdl_trigger_then_wait();
   LLMQRT_TIMELINE_MARK(11);
   __shared__ unsigned s_seq;
-  if (threadIdx.x == 0) s_seq = comm_enter(c);
-  __syncthreads();
-  const unsigned seq = s_seq;                          // 0: the status is raised, the sum is skipped
+  __shared__ int s_ok;
   const int64_t m = blockIdx.x, u = threadIdx.x;
   const bool on = u * 8 < H;
   const int64_t off = m * H;
+  // Everything that does not depend on the peers is requested first: this rank's partial row, the
+  // residual row and (thread 0) the call's sequence number travel to L2 at the same time.
+  uint4 pv = make_uint4(0u, 0u, 0u, 0u);
+  T e[8];
+  if (on) {
+    pv = *reinterpret_cast<const uint4*>(partial + off + u * 8);
+    load_unit<T, true>(x + off, u, e);
+  }
+  if (threadIdx.x == 0) {
+    unsigned sq;
+    s_ok = comm_enter(c, &sq) ? 1 : 0;
+    s_seq = sq;
+  }
+  __syncthreads();
+  const unsigned seq = s_seq;
+  const bool live = s_ok != 0;                         // false: the status is raised, the sum is skipped
   float f[8];
   if (on) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    if (seq != 0u) {
-      const uint4 pv = *reinterpret_cast<const uint4*>(partial + off + u * 8);
+    if (live) {
       // Word placement (any bijection works, as every rank uses the same one): the two words of a
       // thread sit 32 words apart so that each store or poll of a warp covers 512 contiguous bytes.
-      const long long word = m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31), word1 = word + 32;
+      const long long words[2] = {m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31),
+                                  m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31) + 32};
       // One step: every rank sends its row to every rank and all add the W copies themselves (W x the
       // payload leaves each rank).  Two steps, for many ranks: a row goes only to the rank that owns
       // it (rows are dealt out in equal runs), the owner adds the copies and sends the finished row,
@@ -376,24 +392,30 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
       const int rows_per_rank = ((int)gridDim.x + c.world - 1) / c.world;
       const int owner = two_step ? min((int)(m / rows_per_rank), c.world - 1) : c.rank;
       if (two_step) {
-        comm_push_one(c, seq, owner, c.rank, word, make_uint2(pv.x, pv.y));
-        comm_push_one(c, seq, owner, c.rank, word1, make_uint2(pv.z, pv.w));
+        comm_push_one(c, seq, owner, c.rank, words[0], make_uint2(pv.x, pv.y));
+        comm_push_one(c, seq, owner, c.rank, words[1], make_uint2(pv.z, pv.w));
       } else {
-        comm_push(c, seq, word, make_uint2(pv.x, pv.y));
-        comm_push(c, seq, word1, make_uint2(pv.z, pv.w));
+        comm_push(c, seq, words[0], make_uint2(pv.x, pv.y));
+        comm_push(c, seq, words[1], make_uint2(pv.z, pv.w));
       }
       const unsigned long long t0 = comm_timer_ns();
       bool ok = true;
-      for (int s = 0; s < c.world && ok && owner == c.rank; ++s) {
-        uint2 d0, d1;
-        ok = comm_gather(c, seq, s, word, t0, &d0) && comm_gather(c, seq, s, word1, t0, &d1);
+      if (owner == c.rank) {
+        uint4 d[kCommMaxWorld][2];
+        ok = comm_gather_all<kCommMaxWorld, 2>(c, seq, 0, c.world, words, t0, d);
         if (ok) {
-          const T* e0 = reinterpret_cast<const T*>(&d0);
-          const T* e1 = reinterpret_cast<const T*>(&d1);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[j] += to_f32<T>(e0[j]);
-            acc[4 + j] += to_f32<T>(e1[j]);
+          for (int s = 0; s < kCommMaxWorld; ++s) {    // rank order: the same bits on every rank
+            if (s < c.world) {
+              const uint2 p0 = make_uint2(d[s][0].x, d[s][0].z), p1 = make_uint2(d[s][1].x, d[s][1].z);
+              const T* e0 = reinterpret_cast<const T*>(&p0);
+              const T* e1 = reinterpret_cast<const T*>(&p1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                acc[j] += to_f32<T>(e0[j]);
+                acc[4 + j] += to_f32<T>(e1[j]);
+              }
+            }
           }
         }
       }
@@ -404,14 +426,15 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
           for (int j = 0; j < 8; ++j) red[j] = from_f32<T>(acc[j]);
           const uint4 rv = *reinterpret_cast<const uint4*>(red);
           for (int p = 0; p < c.world; ++p) {
-            comm_push_one(c, seq, p, kCommMaxWorld, word, make_uint2(rv.x, rv.y));
-            comm_push_one(c, seq, p, kCommMaxWorld, word1, make_uint2(rv.z, rv.w));
+            comm_push_one(c, seq, p, kCommMaxWorld, words[0], make_uint2(rv.x, rv.y));
+            comm_push_one(c, seq, p, kCommMaxWorld, words[1], make_uint2(rv.z, rv.w));
           }
         }
-        uint2 d0, d1;
-        ok = ok && comm_gather(c, seq, kCommMaxWorld, word, t0, &d0) && comm_gather(c, seq, kCommMaxWorld, word1, t0, &d1);
-        const T* e0 = reinterpret_cast<const T*>(&d0);
-        const T* e1 = reinterpret_cast<const T*>(&d1);
+        uint4 d[1][2];
+        ok = ok && comm_gather_all<1, 2>(c, seq, kCommMaxWorld, 1, words, t0, d);
+        const uint2 p0 = make_uint2(d[0][0].x, d[0][0].z), p1 = make_uint2(d[0][1].x, d[0][1].z);
+        const T* e0 = reinterpret_cast<const T*>(&p0);
+        const T* e1 = reinterpret_cast<const T*>(&p1);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           acc[j] = ok ? to_f32<T>(e0[j]) : 0.f;
@@ -419,8 +442,6 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
         }
       }
     }
-    T e[8];
-    load_unit<T, true>(x + off, u, e);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float r = round_to<T>(acc[j]);                                // the all-reduced value, in T
@@ -431,6 +452,7 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
     if (x_out) store_unit<T, true>(x_out + off, u, e);
   }
   rmsnorm_regs_finish<T>(on, f, m, u, H, weight, eps, y, q, scale_f32);
+  if (threadIdx.x == 0) comm_leave(c, seq);            // after the barriers above: every thread is done with seq
 }
 
 // Cluster size for a row kernel: as many CTAs per row as needed to put about two CTAs on every SM,
@@ -566,12 +588,13 @@ int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x
   }();
   const int two_step = (c->dev.world >= 8 || force_two_step) ? 1 : 0;
   int rc;
-#define LLMQRT_RUN(T)                                                                                              \
-  rc = launch_chained(allreduce_rmsnorm_kernel<T>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,                  \
+#define LLMQRT_RUN(T, MAXT)                                                                                        \
+  rc = launch_chained(allreduce_rmsnorm_kernel<T, MAXT>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,            \
                       (cudaStream_t)stream, 1, c->dev, reinterpret_cast<const T*>(partial),                          \
                       reinterpret_cast<const T*>(x), reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), \
                       eps, reinterpret_cast<T*>(y), q, scale_f32, H, two_step)
-  if (dtype == LLMQRT_F16) LLMQRT_RUN(__half); else LLMQRT_RUN(__nv_bfloat16);
+  if (threads <= 512) { if (dtype == LLMQRT_F16) LLMQRT_RUN(__half, 512); else LLMQRT_RUN(__nv_bfloat16, 512); }
+  else { if (dtype == LLMQRT_F16) LLMQRT_RUN(__half, 1024); else LLMQRT_RUN(__nv_bfloat16, 1024); }
 #undef LLMQRT_RUN
   if (rc) return rc;
   return check_launch("allreduce_rmsnorm");

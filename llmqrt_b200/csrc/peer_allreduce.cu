@@ -26,28 +26,41 @@ peer_allreduce_kernel(CommDev c, const uint2* __restrict__ x, uint2* __restrict_
   pdl_wait();
   pdl_trigger();
   __shared__ unsigned s_seq;
-  if (threadIdx.x == 0) s_seq = comm_enter(c);
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    unsigned seq;
+    s_ok = comm_enter(c, &seq) ? 1 : 0;
+    s_seq = seq;
+  }
   __syncthreads();
   const unsigned seq = s_seq;
-  if (seq == 0u) return;                                               // status raised by an earlier call
-  const long long stride = (long long)gridDim.x * kArThreads;
-  const long long w0 = (long long)blockIdx.x * kArThreads + threadIdx.x;
-  for (long long w = w0; w < nword; w += stride) comm_push(c, seq, w, x[w]);
-  const unsigned long long t0 = comm_timer_ns();
-  for (long long w = w0; w < nword; w += stride) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < c.world; ++s) {
-      uint2 d;
-      if (!comm_gather(c, seq, s, w, t0, &d)) return;
-      const T* e = reinterpret_cast<const T*>(&d);
+  if (s_ok) {                                                          // else: status raised by an earlier call
+    const long long stride = (long long)gridDim.x * kArThreads;
+    const long long w0 = (long long)blockIdx.x * kArThreads + threadIdx.x;
+    for (long long w = w0; w < nword; w += stride) comm_push(c, seq, w, x[w]);
+    const unsigned long long t0 = comm_timer_ns();
+    for (long long w = w0; w < nword; w += stride) {
+      uint4 d[kCommMaxWorld][1];
+      const long long words[1] = {w};
+      if (!comm_gather_all<kCommMaxWorld, 1>(c, seq, 0, c.world, words, t0, d)) break;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[j] += to_f32<T>(e[j]);
+      for (int s = 0; s < kCommMaxWorld; ++s) {                        // rank order: identical bits everywhere
+        if (s < c.world) {
+          const uint2 pl = make_uint2(d[s][0].x, d[s][0].z);
+          const T* e = reinterpret_cast<const T*>(&pl);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[j] += to_f32<T>(e[j]);
+        }
+      }
+      __align__(8) T r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = from_f32<T>(acc[j]);
+      out[w] = *reinterpret_cast<const uint2*>(r);
     }
-    __align__(8) T r[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r[j] = from_f32<T>(acc[j]);
-    out[w] = *reinterpret_cast<const uint2*>(r);
   }
+  __syncthreads();
+  if (threadIdx.x == 0) comm_leave(c, seq);
 }
 
 }  // namespace

@@ -14,8 +14,9 @@
 // Two parities: a rank can run at most one call ahead of a peer (it cannot finish call k+1 before
 // that peer has pushed for k+1, which the peer does after finishing call k), so call k+1 never
 // overwrites words a peer still reads for call k, and a stale word always carries an older tag.
-// The sequence number lives in the buffer and is advanced once per call by the block that draws the
-// last ticket (after every block has read it), so a call can be replayed from a CUDA graph.
+// The sequence number of the last completed call lives in the buffer; a call uses the next one and
+// the block that finishes last publishes it (every block has used it by then), so a call can be
+// replayed from a CUDA graph.
 // Polls are bounded (5 s unless the host sets another limit): on a time-out the sticky status word of
 // the buffer is raised and later calls return without waiting.
 #pragma once
@@ -60,19 +61,31 @@ __device__ __forceinline__ unsigned long long comm_timer_ns() {
   return t;
 }
 
-// Start of a call, ONE thread per block: returns the call's sequence number, or 0 when the status
-// word is raised (the caller then neither pushes nor polls).  The block that draws the last ticket
-// knows that every block has read the old number and advances it.
-__device__ __forceinline__ unsigned comm_enter(const CommDev& c) {
-  unsigned* ctrl = reinterpret_cast<unsigned*>(c.base[c.rank]);          // [0] sequence, [1] status, [2] ticket
-  const unsigned seq = *reinterpret_cast<volatile unsigned*>(ctrl) + 1u;
-  const bool bad = *reinterpret_cast<volatile unsigned*>(ctrl + 1) != 0u;
-  __threadfence();                                                       // the reads above before the ticket below
+// Sequence numbers run 1, 2, ..., 0xFFFFFFFE, 1, ...: never 0 (the tag of a buffer that was never
+// written) and with alternating parity across the wrap (0xFFFFFFFE is even, 1 is odd).
+__device__ __forceinline__ unsigned comm_next_seq(unsigned s) { return s >= 0xFFFFFFFEu ? 1u : s + 1u; }
+
+// Start of a call, ONE thread per block: reads the call's sequence number (one more than the last
+// completed call's) and whether the sticky status is raised (the caller then neither pushes nor
+// polls).  Nothing is written here, so the block's first stores do not wait for an atomic.
+__device__ __forceinline__ bool comm_enter(const CommDev& c, unsigned* seq) {
+  const unsigned* ctrl = reinterpret_cast<const unsigned*>(c.base[c.rank]);   // [0] sequence, [1] status, [2] ticket
+  const unsigned last = *reinterpret_cast<const volatile unsigned*>(ctrl);
+  const unsigned bad = *reinterpret_cast<const volatile unsigned*>(ctrl + 1);
+  *seq = comm_next_seq(last);
+  return bad == 0u;
+}
+
+// End of a call, ONE thread per block, after the block's last use of the sequence number: the block
+// that draws the last ticket publishes the number as completed.  The next call on this rank is
+// ordered after this kernel by the stream, so it reads the advanced number; a CUDA graph replays.
+__device__ __forceinline__ void comm_leave(const CommDev& c, unsigned seq) {
+  unsigned* ctrl = reinterpret_cast<unsigned*>(c.base[c.rank]);
+  __threadfence();
   if (atomicAdd(ctrl + 2, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) {
     ctrl[2] = 0u;
     *reinterpret_cast<volatile unsigned*>(ctrl) = seq;
   }
-  return bad ? 0u : seq;
 }
 
 // Stores one tagged word (eight payload bytes) into slot (parity of seq, me) of every rank.
@@ -103,6 +116,41 @@ __device__ __forceinline__ bool comm_gather(const CommDev& c, unsigned seq, int 
     v = comm_ld_v4(src);
   }
   *payload = make_uint2(v.x, v.z);
+  return true;
+}
+
+// The same for NW words of each of the slots first_slot .. first_slot + nslots - 1 (nslots <= NS) at
+// once: all loads of a round are issued before any tag is looked at, so a round costs one trip to L2
+// however many sources there are (polling them one after the other costs one trip each even when
+// every word has long arrived).  words[j] are the word indices; on success v[i][j] holds the tagged
+// word of slot first_slot + i, word j: payload in .x and .z.
+template <int NS, int NW>
+__device__ __forceinline__ bool comm_gather_all(const CommDev& c, unsigned seq, int first_slot, int nslots,
+                                                const long long (&words)[NW], unsigned long long t0,
+                                                uint4 (&v)[NS][NW]) {
+  volatile unsigned* status = reinterpret_cast<unsigned*>(c.base[c.rank]) + 1;
+  const uint4* slot0 = comm_slot(c.base[c.rank], c.slot_bytes, (int)(seq & 1u), first_slot);
+  const long long slot_words = c.slot_bytes / 16;
+  unsigned pending = 0u;                              // bit (i * NW + j): word not yet seen
+#pragma unroll
+  for (int i = 0; i < NS; ++i)
+    if (i < nslots) pending |= ((1u << NW) - 1u) << (i * NW);
+  for (unsigned it = 1; pending != 0u; ++it) {
+#pragma unroll
+    for (int i = 0; i < NS; ++i)
+#pragma unroll
+      for (int j = 0; j < NW; ++j)
+        if (pending >> (i * NW + j) & 1u) v[i][j] = comm_ld_v4(slot0 + i * slot_words + words[j]);
+#pragma unroll
+    for (int i = 0; i < NS; ++i)
+#pragma unroll
+      for (int j = 0; j < NW; ++j)
+        if ((pending >> (i * NW + j) & 1u) && v[i][j].y == seq && v[i][j].w == seq) pending &= ~(1u << (i * NW + j));
+    if (pending != 0u && (it & 63u) == 0u && (*status != 0u || comm_timer_ns() - t0 > c.poll_limit_ns)) {
+      *status = 1u;
+      return false;
+    }
+  }
   return true;
 }
 

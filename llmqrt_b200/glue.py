@@ -21,11 +21,13 @@ def rmsnorm(x, weight, eps: float, residual=None, quantize: bool = False, want_y
     x2 = x.reshape(-1, H).contiguous()
     M = x2.shape[0]
     r2 = residual.reshape(-1, H).contiguous() if residual is not None else None
+    if comm is not None and r2 is not None and r2.data_ptr() % 16:
+        r2 = r2.clone()                                  # rank-local misalignment must not change the path
     h = torch.empty_like(x2) if residual is not None else None
     y = torch.empty_like(x2) if want_y else None
     q = torch.empty((M, H), dtype=torch.int8, device=dev) if quantize else None
     s = torch.empty(M, dtype=torch.float32, device=dev) if quantize else None
-    fused = comm is not None and r2 is not None and H % 8 == 0 and H <= 8192 and comm.eligible(r2)
+    fused = comm is not None and r2 is not None and comm.eligible(r2) and comm.fits_rows(M, H)
     if comm is not None and r2 is not None and not fused:
         torch.distributed.all_reduce(r2, group=comm.group)
     with torch.cuda.device(dev):

@@ -101,13 +101,15 @@ class FP8DynamicLinear(_FP8Base):
         if self.per_tensor:
             qx, x_scale = ops.quantize_fp8(x2, per_token=False)
             alpha = self.weight_scale.data.reshape(1) * x_scale                 # stays on the device
-            out = ops.fp8_linear_tensorwise(qx, qw, self._bias_for(self.dtype), alpha, 1.0, self.dtype)
+            out = ops.fp8_linear_tensorwise(qx, qw, self._bias_for(self.dtype), alpha, 1.0, self.dtype,
+                                            static_weight=True)
         else:
             qx, x_scale = ops.quantize_fp8(x2, per_token=True)
             bias = self.bias.data if self.bias is not None else None
             if bias is not None and bias.dtype not in (torch.bfloat16, torch.float32):
                 bias = bias.float()
-            out = ops.fp8_linear_rowwise(qx, qw, bias, x_scale, self.weight_scale.data.reshape(1, -1))
+            out = ops.fp8_linear_rowwise(qx, qw, bias, x_scale, self.weight_scale.data.reshape(1, -1),
+                                         static_weight=True)
         return out.to(x.dtype).view(*x_shape[:-1], -1)
 
 
@@ -150,7 +152,8 @@ class FP8StaticLinear(_FP8Base):
         x2 = x.reshape(-1, x_shape[-1])
         qx = ops.quantize_fp8_static(x2, self.input_scale.data)
         alpha = self.weight_scale.data.reshape(1) * self.input_scale.data.reshape(1)
-        out = ops.fp8_linear_tensorwise(qx, self._fp8_weight(), self._bias_for(self.dtype), alpha, 1.0, self.dtype)
+        out = ops.fp8_linear_tensorwise(qx, self._fp8_weight(), self._bias_for(self.dtype), alpha, 1.0, self.dtype,
+                                        static_weight=True)
         out = out.view(*x_shape[:-1], -1)
         if self.quantize_output:
             qout = ops.quantize_fp8_static(out, self.output_scale.data).view(out.shape)

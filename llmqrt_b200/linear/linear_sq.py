@@ -79,7 +79,7 @@ class SqW8A8BBF16OBF16PerTensor(LinearBase):
         if x2.shape[0] == 0:
             return torch.zeros(*x_shape[:-1], self.out_features, dtype=x.dtype, device=x.device)
         qx, _, alpha = ops.quantize_int8(x2, per_token=False, scale_mul=self._weight_scale_value())
-        y = ops.int8_linear_per_tensor(qx, self.qweight, self._bias_as_f16(x.device), alpha, 1.0)
+        y = ops.int8_linear_per_tensor(qx, self.qweight, self._bias_as_f16(x.device), alpha, 1.0, static_weight=True)
         return y.to(x.dtype).view(*x_shape[:-1], -1)
 
     @classmethod
@@ -132,12 +132,14 @@ class SqW8A8BBF16OBF16PerChannel(LinearBase):
         if x2.shape[0] == 0:
             return torch.zeros(*x_shape[:-1], self.out_features, dtype=x.dtype, device=x.device)
         qx, _, a_scale = ops.quantize_int8(x2, per_token=True)
-        y = ops.int8_linear_per_channel(qx, self.qweight, self.bias, a_scale, self.weight_scale, x.dtype)
+        y = ops.int8_linear_per_channel(qx, self.qweight, self.bias, a_scale, self.weight_scale, x.dtype,
+                                        static_weight=True)
         return y.view(*x_shape[:-1], -1)
 
     def forward_quantized(self, qx: torch.Tensor, a_scale: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """GEMM + epilogue on activations a fused producer kernel has already quantized."""
-        return ops.int8_linear_per_channel(qx, self.qweight, self.bias, a_scale, self.weight_scale, out_dtype)
+        return ops.int8_linear_per_channel(qx, self.qweight, self.bias, a_scale, self.weight_scale, out_dtype,
+                                           static_weight=True)
 
     @classmethod
     def from_linear(cls, module: torch.nn.Linear, w_bit, group_size, init_only=True, dtype=torch.float16,

@@ -65,7 +65,17 @@ def quantize_fp8_static(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 
 # ---------------------------------------------------------------------------------------------
 # W8A8 GEMMs.  `w` is always the [N, K] row-major weight.
+#
+# static_weight=True tells the kernel that `w` is a stored weight that nothing queued on the stream
+# writes; it may then fetch the first weight tiles while the preceding kernel is still running.  The
+# default waits for the preceding kernel before reading anything, so quantizing `w` on the same
+# stream right before the call is safe.  The Linear modules and the decoder, whose weights are
+# buffers prepared long before, pass True.
 # ---------------------------------------------------------------------------------------------
+def _flags(static_weight: bool) -> int:
+    return L.GEMM_STATIC_WEIGHT if static_weight else 0
+
+
 def _alpha_args(alpha, dev):
     """A Python number travels by value; a tensor is read on the device (no host sync)."""
     if isinstance(alpha, torch.Tensor):
@@ -76,7 +86,7 @@ def _alpha_args(alpha, dev):
     return float(alpha), None
 
 
-def int8_linear_per_tensor(a, w, bias, alpha, beta: float) -> torch.Tensor:
+def int8_linear_per_tensor(a, w, bias, alpha, beta: float, static_weight: bool = False) -> torch.Tensor:
     dev = L.require_cuda(a, w, bias)
     M, K = a.shape
     N = w.shape[0]
@@ -84,11 +94,12 @@ def int8_linear_per_tensor(a, w, bias, alpha, beta: float) -> torch.Tensor:
     av, ad = _alpha_args(alpha, dev)
     with torch.cuda.device(dev):
         L.call("llmqrt_w8a8_int8_linear_per_tensor", L.ptr(a), a.stride(0), L.ptr(w), w.stride(0), L.ptr(bias), av,
-               L.ptr(ad), float(beta), L.ptr(out), N, M, N, K, L.ptr(L.workspace(dev)), L.stream(dev))
+               L.ptr(ad), float(beta), L.ptr(out), N, M, N, K, L.ptr(L.workspace(dev)), L.stream(dev),
+               _flags(static_weight))
     return out
 
 
-def int8_linear_per_channel(a, w, bias, a_scale, w_scale, out_dtype) -> torch.Tensor:
+def int8_linear_per_channel(a, w, bias, a_scale, w_scale, out_dtype, static_weight: bool = False) -> torch.Tensor:
     dev = L.require_cuda(a, w, bias, a_scale, w_scale)
     M, K = a.shape
     N = w.shape[0]
@@ -100,22 +111,22 @@ def int8_linear_per_channel(a, w, bias, a_scale, w_scale, out_dtype) -> torch.Te
     with torch.cuda.device(dev):
         L.call("llmqrt_w8a8_int8_linear_per_channel", L.ptr(a), a.stride(0), L.ptr(w), w.stride(0), L.ptr(bias),
                L.dtype_code(bias.dtype) if bias is not None else L.F16, L.ptr(a_s), L.ptr(w_s), L.ptr(out),
-               L.dtype_code(out_dtype), N, M, N, K, L.ptr(L.workspace(dev)), L.stream(dev))
+               L.dtype_code(out_dtype), N, M, N, K, L.ptr(L.workspace(dev)), L.stream(dev), _flags(static_weight))
     return out
 
 
-def int8_gemm_s32(a, w) -> torch.Tensor:
+def int8_gemm_s32(a, w, static_weight: bool = False) -> torch.Tensor:
     dev = L.require_cuda(a, w)
     M, K = a.shape
     N = w.shape[0]
     out = torch.empty((M, N), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         L.call("llmqrt_w8a8_int8_gemm_s32", L.ptr(a), a.stride(0), L.ptr(w), w.stride(0), L.ptr(out), N, M, N, K,
-               L.ptr(L.workspace(dev)), L.stream(dev))
+               L.ptr(L.workspace(dev)), L.stream(dev), _flags(static_weight))
     return out
 
 
-def fp8_linear_tensorwise(a, w, bias, alpha, beta: float, out_dtype) -> torch.Tensor:
+def fp8_linear_tensorwise(a, w, bias, alpha, beta: float, out_dtype, static_weight: bool = False) -> torch.Tensor:
     dev = L.require_cuda(a, w, bias)
     M, K = a.shape
     N = w.shape[0]
@@ -124,11 +135,11 @@ def fp8_linear_tensorwise(a, w, bias, alpha, beta: float, out_dtype) -> torch.Te
     with torch.cuda.device(dev):
         L.call("llmqrt_f8f8_tensorwise", L.ptr(a), L.dtype_code(a.dtype), a.stride(0), L.ptr(w), w.stride(0),
                L.ptr(bias), av, L.ptr(ad), float(beta), L.ptr(out), L.dtype_code(out_dtype), N, M, N, K,
-               L.ptr(L.workspace(dev)), L.stream(dev))
+               L.ptr(L.workspace(dev)), L.stream(dev), _flags(static_weight))
     return out
 
 
-def fp8_linear_rowwise(a, w, bias, x_scale, w_scale) -> torch.Tensor:
+def fp8_linear_rowwise(a, w, bias, x_scale, w_scale, static_weight: bool = False) -> torch.Tensor:
     dev = L.require_cuda(a, w, bias, x_scale, w_scale)
     M, K = a.shape
     N = w.shape[0]
@@ -138,7 +149,7 @@ def fp8_linear_rowwise(a, w, bias, x_scale, w_scale) -> torch.Tensor:
     with torch.cuda.device(dev):
         L.call("llmqrt_f8f8bf16_rowwise", L.ptr(a), L.dtype_code(a.dtype), a.stride(0), L.ptr(w), w.stride(0),
                L.ptr(bias), L.dtype_code(bias.dtype) if bias is not None else L.BF16, L.ptr(xs), L.ptr(ws),
-               L.ptr(out), N, M, N, K, L.ptr(L.workspace(dev)), L.stream(dev))
+               L.ptr(out), N, M, N, K, L.ptr(L.workspace(dev)), L.stream(dev), _flags(static_weight))
     return out
 
 

@@ -161,7 +161,7 @@ class Qwen2Decoder:
                                             comm=self.comm)
             if h_new is not None:
                 h = h_new
-            qkv = ops.int8_linear_per_channel(xq, L_.wqkv, L_.bqkv, xs, L_.sqkv, dt)          # [M, nq + 2 nkv]
+            qkv = ops.int8_linear_per_channel(xq, L_.wqkv, L_.bqkv, xs, L_.sqkv, dt, True)          # [M, nq + 2 nkv]
             qkv4 = qkv.view(B, S, self.hq + 2 * self.hkv, d)
             q, k, v = qkv4[:, :, :self.hq], qkv4[:, :, self.hq:self.hq + self.hkv], qkv4[:, :, self.hq + self.hkv:]
             kc, vc = L_.k_cache[batch0:batch0 + B], L_.v_cache[batch0:batch0 + B]
@@ -178,14 +178,14 @@ class Qwen2Decoder:
                 glue.rope_kv_write(q, k, v, self.cos, self.sin, pos0=self.pos, pos_dev=None, k_cache=kc, v_cache=vc)
                 attn = attention.flash_attn_func(q, k, v, causal=True)
                 aq, _, a_s = ops.quantize_int8(attn.reshape(B * S, nq), per_token=True)
-            o = ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt)
+            o = ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt, True)
             if self.comm is None:
                 o = self._allreduce(o)
             _, h, yq, ys = glue.rmsnorm(h, L_.ln2, cfg.rms_eps, residual=o, quantize=True, want_y=False,
                                         comm=self.comm)
-            gu = ops.int8_linear_per_channel(yq, L_.wgu, None, ys, L_.sgu, dt)                # [M, 2 I_local]
+            gu = ops.int8_linear_per_channel(yq, L_.wgu, None, ys, L_.sgu, dt, True)                # [M, 2 I_local]
             _, mq, ms = glue.silu_mul(gu, quantize=True, want_y=False)
-            pending = ops.int8_linear_per_channel(mq, L_.wd, None, ms, L_.sd, dt)
+            pending = ops.int8_linear_per_channel(mq, L_.wd, None, ms, L_.sd, dt, True)
             if self.comm is None:
                 pending = self._allreduce(pending)
         return h, pending

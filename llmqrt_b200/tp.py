@@ -93,15 +93,37 @@ class PeerAllreduce:
         return self._comm
 
     def eligible(self, x: torch.Tensor) -> bool:
-        return (x.is_contiguous() and x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0
-                and x.numel() * 2 <= self.max_bytes and x.data_ptr() % 16 == 0)
+        """Whether `x` goes over the peer buffers.  Depends on dtype and element count only -- facts
+        every rank shares -- so all ranks take the same path (a rank that chose NCCL while the others
+        polled the buffers would stall them until the wait limit)."""
+        return x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0 and x.numel() * 2 <= self.max_bytes
+
+    def fits_rows(self, M: int, H: int) -> bool:
+        """Capacity rule of llmqrt_comm_allreduce_rmsnorm: a row occupies one tagged 16-byte word per
+        four values, with the row's thread count rounded up to whole warps."""
+        threads = (H // 8 + 31) // 32 * 32
+        return H % 8 == 0 and H <= 8192 and M * threads * 32 <= 2 * ((self.max_bytes + 255) // 256 * 256)
 
     def allreduce(self, x: torch.Tensor) -> torch.Tensor:
+        """In-place sum over the group.  A tensor that is not contiguous or not 16-byte aligned (a
+        rank-local accident) is staged through an aligned copy rather than sent down another path."""
         L = self._L
+        buf = x if (x.is_contiguous() and x.data_ptr() % 16 == 0) else x.contiguous().clone()
         with torch.cuda.device(self.device):
-            L.call("llmqrt_comm_allreduce", self._comm, L.ptr(x), L.ptr(x), L.dtype_code(x.dtype), x.numel(),
+            L.call("llmqrt_comm_allreduce", self._comm, L.ptr(buf), L.ptr(buf), L.dtype_code(x.dtype), x.numel(),
                    L.stream(self.device))
+        if buf is not x:
+            x.copy_(buf)
         return x
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's.  Collective: every rank calls it, after its
+        last all-reduce has completed (the barrier makes sure no peer still writes into the buffer)."""
+        if self._comm is not None and self._comm.value:
+            torch.cuda.synchronize(self.device)
+            torch.distributed.barrier(group=self.group)
+            self._L.call("llmqrt_comm_destroy", self._comm)
+            self._comm = None
 
     def set_poll_limit_ms(self, ms: int) -> None:
         """Bound of the waits on peers for calls launched (or graphs captured) from now on."""

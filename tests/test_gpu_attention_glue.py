@@ -65,6 +65,30 @@ def test_prefill_full_size_properties():
     assert max_abs(out[:, :300], part) < 1e-3
 
 
+def test_prefill_full_size_against_oracle():
+    # batch 4 x 2048 tokens, 28/4 heads, head_dim 128, causal: sampled (batch, head, query row) triples,
+    # among them the rows around the tile boundaries and the last one, against the fp64 oracle
+    from llmqrt_b200.attention import flash_attn_func
+    from oracle import attention as oa
+    B, S, Hq, Hkv, d = 4, 2048, 28, 4, 128
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(B, S, Hq, d, generator=g).to(torch.float16)
+    k = torch.randn(B, S, Hkv, d, generator=g).to(torch.float16)
+    v = torch.randn(B, S, Hkv, d, generator=g).to(torch.float16)
+    out = flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=True).cpu()
+    rows = [0, 1, 63, 64, 127, 128, 129, 255, 256, 1023, 1024, 2046, 2047] + \
+        torch.randint(0, S, (19,), generator=g).tolist()
+    worst = 0.0
+    for b in range(B):
+        for h in (0, 6, 7, 13, 27):
+            hk = h // (Hq // Hkv)
+            for r in rows:
+                ref = oa.attention_prefill(q[b:b + 1, r:r + 1, h:h + 1], k[b:b + 1, :r + 1, hk:hk + 1],
+                                           v[b:b + 1, :r + 1, hk:hk + 1], causal=True)
+                worst = max(worst, max_abs(out[b, r, h], ref[0, 0, 0]))
+    assert worst < ATTN_TOL
+
+
 # ------------------------------------------------------------------ decode
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B,Hq,Hkv,d,Smax,lens", [
@@ -93,8 +117,8 @@ def test_decode_with_append(dtype, B, Hq, Hkv, d, Smax, lens):
 
 
 def test_decode_config_shape_long_contexts():
-    # batch 32, 28/4 heads, head_dim 128, context lengths uniform in [512, 8192]; checked against the
-    # oracle on a subset of sequences (the oracle is O(L) per sequence and slow) and for finiteness on all
+    # batch 32, 28/4 heads, head_dim 128, context lengths uniform in [512, 8192]; every sequence is
+    # checked against the oracle
     from llmqrt_b200.attention import attn_decode
     from oracle import attention as oa
     B, Hq, Hkv, d, Smax = 32, 28, 4, 128, 8192
@@ -105,10 +129,11 @@ def test_decode_config_shape_long_contexts():
     lens = torch.randint(512, 8193, (B,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
     out = attn_decode(q, kc, vc, lens.cuda(), Smax)
     assert torch.isfinite(out.float()).all()
-    for b in (0, 7, 31):
-        ref = oa.attention_decode_kvcache(q[b:b + 1].cpu().unsqueeze(1), kc[b:b + 1].cpu(), vc[b:b + 1].cpu(), None,
-                                          None, lens[b:b + 1])
-        assert max_abs(out[b], ref[0, 0]) < ATTN_TOL
+    for b in range(B):
+        L_b = int(lens[b])
+        ref = oa.attention_decode_kvcache(q[b:b + 1].cpu().unsqueeze(1), kc[b:b + 1, :L_b].cpu(), vc[b:b + 1, :L_b].cpu(),
+                                          None, None, lens[b:b + 1])
+        assert max_abs(out[b], ref[0, 0]) < ATTN_TOL, b
     out2 = attn_decode(q, kc, vc, lens.cuda(), Smax)
     assert bits_equal(out, out2)                                            # fixed combine order: repeatable
 
@@ -171,6 +196,31 @@ def test_decode_with_rotary_and_append_in_kernel(dtype, Hq, Hkv, d, lens, Smax):
                                    v=rows[:, Hq + Hkv:].unsqueeze(1), rotary_cos=cos, rotary_sin=sin,
                                    cache_seqlens=seqlens - 1, rotary_interleaved=False, max_seqlen_k=Smax)
     assert bits_equal(out2[:, 0], got) and bits_equal(kc2, kc)
+
+
+def test_decode_append_on_a_full_cache_writes_nothing():
+    # cache_seqlens == capacity: there is no row left for the new token.  The kernels clamp: nothing is
+    # written (the guard rows behind the cache stay intact) and the sequence attends over the full cache.
+    from llmqrt_b200.attention import attn_decode, flash_attn_with_kvcache
+    B, Hq, Hkv, d, cap = 2, 8, 2, 128, 96
+    g = torch.Generator().manual_seed(13)
+    big_k = torch.randn(B + 1, cap, Hkv, d, generator=g).half().cuda()     # sequence b + 1 guards sequence b
+    big_v = torch.randn(B + 1, cap, Hkv, d, generator=g).half().cuda()
+    kc, vc = big_k[:B], big_v[:B]
+    k0, v0 = big_k.clone(), big_v.clone()
+    q = torch.randn(B, 1, Hq, d, generator=g).half().cuda()
+    kn = torch.randn(B, 1, Hkv, d, generator=g).half().cuda()
+    vn = torch.randn(B, 1, Hkv, d, generator=g).half().cuda()
+    cos = torch.ones(cap, d // 2, device="cuda")
+    sin = torch.zeros(cap, d // 2, device="cuda")
+    full = torch.full((B,), cap, dtype=torch.int32, device="cuda")
+    for rotary in (False, True):
+        kw = dict(rotary_cos=cos, rotary_sin=sin, rotary_interleaved=False) if rotary else {}
+        out = flash_attn_with_kvcache(q, kc, vc, k=kn, v=vn, cache_seqlens=full, causal=True, **kw)
+        torch.cuda.synchronize()
+        assert bits_equal(big_k, k0) and bits_equal(big_v, v0)
+        want = attn_decode(q[:, 0], kc, vc, full, cap)
+        assert max_abs(out[:, 0], want) < ATTN_TOL
 
 
 def test_decode_quantization_single_split_without_workspace():

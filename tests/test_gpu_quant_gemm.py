@@ -109,6 +109,21 @@ def test_int8_accumulators_bit_exact(ops, path, M, N, K):
     assert torch.equal(acc.cpu(), og.int8_accumulate(a, w))
 
 
+# Prefill-sized M: the four Qwen2-0.5B linears at M = 4096, and one Qwen2-7B shape at M = 16384 (the
+# token count of a 16 x 1024 prefill chunk, 128 x 256 tiles, persistent schedule).  The fp64 oracle is
+# evaluated on a few hundred sampled rows so that it stays a matter of seconds.
+@pytest.mark.parametrize("M,N,K", [(4096, 896, 896), (4096, 128, 896), (4096, 4864, 896), (4096, 896, 4864),
+                                   (16384, 4608, 3584)])
+def test_int8_accumulators_bit_exact_prefill_sizes(ops, M, N, K):
+    from oracle import gemm as og
+    g = torch.Generator().manual_seed(M + N * 3 + K)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    w = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
+    acc = ops.int8_gemm_s32(a.cuda(), w.cuda()).cpu()
+    rows = torch.cat([torch.tensor([0, 127, 128, M - 1]), torch.randperm(M, generator=g)[:252]])
+    assert torch.equal(acc[rows], og.int8_accumulate(a[rows], w))
+
+
 @pytest.mark.parametrize("path", list(PATHS))
 def test_int8_gemm_is_repeatable_with_split_k(ops, path):
     # split-K partials live in a shared workspace whose counters must return to zero
@@ -194,6 +209,45 @@ def test_fp8_rowwise_sweep(ops, path, M, N, K):
                                w_scale.reshape(1, -1).cuda())
     y_ref = og.fp8_linear_rowwise(xq, wq, bias, x_scale, w_scale.reshape(1, -1))
     assert rel_fro(y, y_ref) < 1e-2
+
+
+@pytest.mark.parametrize("N,K", FP8_SHAPES)
+def test_fp8_rowwise_m4096(ops, N, K):
+    # the largest M of the FP8 sweep configuration; epilogue order of
+    # runtime/csrc/fp8/sm89_fp8_rowwise_fbgemm.cu:193-245
+    from oracle import gemm as og
+    from oracle import quant as oq
+    M = 4096
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    wq, w_scale = oq.quantize_weight_fp8_per_channel(w)
+    xq, x_scale = oq.quantize_fp8(x, per_token=True)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16) if N in (896, 128) else None
+    y = ops.fp8_linear_rowwise(xq.cuda(), wq.cuda(), None if bias is None else bias.cuda(), x_scale.cuda(),
+                               w_scale.reshape(1, -1).cuda())
+    rows = torch.cat([torch.tensor([0, 127, 128, M - 1]), torch.randperm(M, generator=g)[:508]])
+    y_ref = og.fp8_linear_rowwise(xq[rows], wq, bias, x_scale[rows], w_scale.reshape(1, -1))
+    assert rel_fro(y[rows.cuda()], y_ref) < 1e-2
+    assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("M", [64, 256, 4096])
+def test_weight_quantized_right_before_the_gemm(ops, M):
+    # Without LLMQRT_GEMM_STATIC_WEIGHT the GEMM must not read W before the kernel in front of it on
+    # the stream has finished: here that kernel is the library's own quantizer producing W.
+    from oracle import gemm as og
+    g = torch.Generator().manual_seed(M)
+    N, K = 1024, 2048
+    x = torch.randn(M, K, generator=g).to(torch.float16).cuda()
+    w = torch.randn(N, K, generator=g).to(torch.float16).cuda()
+    for _ in range(3):
+        wq_stale = torch.zeros(N, K, dtype=torch.int8, device="cuda")     # what an early read would see
+        xq, _, _ = ops.quantize_int8(x, per_token=True)
+        wq, _, _ = ops.quantize_int8(w, per_token=True)
+        acc = ops.int8_gemm_s32(xq, wq)
+        del wq_stale
+        assert torch.equal(acc.cpu(), og.int8_accumulate(xq.cpu(), wq.cpu()))
 
 
 @pytest.mark.parametrize("path", list(PATHS))

@@ -40,6 +40,20 @@ def test_package_does_not_import_the_oracle():
                 assert "tests.golden" not in src and "_work/" not in src, f
 
 
+def test_reference_module_names_resolve_to_this_package():
+    # runtime/csrc/bindings.cpp:7-14 is imported as runtime.sq_fp8_kernels (linear_sq.py:14,
+    # linear_fp8.py:7-8); the AWQ kernels as runtime.triton_kernels.awq_kernels (linear_awq.py:14)
+    code = ("import llmqrt_b200, sys; names = llmqrt_b200.install_reference_aliases(); "
+            "from runtime.sq_fp8_kernels import w8a8_int8_linear_bbf16_obf16_per_tensor, "
+            "cutlass_f8f8bf16_tensorwise_sm89, cutlass_f8f8bf16_rowwise_sm89; "
+            "from runtime.triton_kernels.awq_kernels import awq_gemm_triton, awq_dequantize_triton; "
+            "import runtime.sq_fp8_kernels as m; import llmqrt_b200.sq_fp8_kernels as ours; "
+            "assert m is ours and 'runtime.sq_fp8_kernels' in names; "
+            "assert awq_gemm_triton.__module__ == 'llmqrt_b200.triton_kernels.awq_kernels'; print('ok')")
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert p.returncode == 0 and p.stdout.strip().endswith("ok"), p.stdout + p.stderr
+
+
 def test_head_assignment_partitions_heads():
     from llmqrt_b200.tp import head_assignment
     for hq, hkv in ((28, 4), (14, 2), (12, 2), (32, 8)):

@@ -55,8 +55,13 @@ def test_no_alloc_entry_matches_regular_entry_twice_in_a_row():
         L.set_gemm_path(0)
     # and against the default dispatch (tcgen05 above 16 rows): still the same bits
     a, w, bias, a_s, w_s = _case(64, 3584, 3584, 2, True, torch.bfloat16)
-    assert torch.equal(_noalloc(a, w, bias, a_s, w_s, torch.bfloat16).view(torch.int16),
+    got = _noalloc(a, w, bias, a_s, w_s, torch.bfloat16)
+    assert torch.equal(got.view(torch.int16),
                        ops.int8_linear_per_channel(a, w, bias, a_s, w_s, torch.bfloat16).view(torch.int16))
+    # and directly against the CPU oracle of the operator (same fp32 op order: identical bits)
+    from oracle import gemm as og
+    want = og.int8_linear_per_channel(a.cpu(), w.cpu(), bias.cpu(), a_s.cpu(), w_s.cpu(), torch.bfloat16)
+    assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
 
 
 def test_no_alloc_entry_rejects_what_does_not_fit():
