@@ -1,36 +1,92 @@
-// Prefill attention over the new tokens: O = softmax(mask(Q K^T / sqrt(d))) V, causal, GQA.
+// Prefill attention over the new tokens on the 5th-generation tensor cores:
+//     O = softmax(mask(Q K^T / sqrt(d))) V,  causal or not, GQA (query head h reads KV head h / (Hq/Hkv)).
 //
-// Flash-attention style single pass: a block owns 64 query rows of one head (16 per warp), walks
-// the keys in tiles of 64 that are double-buffered in shared memory with cp.async, keeps S, P and
-// O in registers and never writes the score matrix.  Shared-memory rows are XOR-swizzled in
-// 16-byte chunks so that cp.async stores and ldmatrix loads are conflict free.  Query tiles are
-// issued heaviest first (causal tiles near the end of the sequence see the most keys).
-#include "common.cuh"
+// One CTA owns 256 consecutive query rows of one head as two 128-row tiles.  Roles (320 threads):
+//   warps 0-3 / 4-7  one softmax group per query tile, one thread per query row;
+//   warp 8           TMA producer: the two Q tiles once, then K and V tiles of 128 keys through a ring;
+//   warp 9           owns tensor memory; its lane 0 issues every tcgen05.mma.
+// Per key tile j and query tile w:
+//   S_w = Q_w K_j^T    tcgen05.mma kind::f16, both operands K-major in shared memory (TMA, 128-byte
+//                      swizzle), 128 x 128 fp32 accumulator in tensor memory;
+//   softmax            the row's thread reads S with tcgen05.ld (two passes: maximum, then exponentials),
+//                      keeps the running maximum and sum in registers and writes P as packed 16-bit
+//                      pairs back into tensor memory over the first half of S (tcgen05.st);
+//   O_j = P V_j        tcgen05.mma with P as the tensor-memory operand and V as an MN-major
+//                      shared-memory operand (V tiles are stored [key][d], d contiguous); a fresh
+//                      128 x d accumulator per key tile.
+// The row's thread adds O_j into its register accumulator, o = o * exp2(m_old - m_new) + O_j, so the
+// accumulator in tensor memory never has to be rescaled.  The tensor pipe alternates between the two
+// query tiles: while one group runs its softmax, the pipe multiplies for the other.
+//
+// Tensor memory (512 columns): S_0 | S_1 | O_0 | O_1, 128 columns each (O uses d).  P_w aliases the
+// first 64 columns of S_w; the MMAs of one CTA execute in issue order, and S_w(j+1) is only issued
+// after P_w(j) V_j, so the alias is never overwritten while it is being read.
+//
+// Every wait on an mbarrier is bounded; when one runs out the block raises a flag, every role
+// leaves its loop, outstanding copies are drained, tensor memory is freed and a status word is set.
+// No multicast: every CTA fetches its own tiles.
+#include "tc_primitives.cuh"
+
+#include <mutex>
 
 namespace llmqrt {
 namespace {
 
-// 4 warps x 16 query rows, key tiles of 64 (128 rows with 8 warps was measured 30 % slower: one
-// block per SM instead of three)
-constexpr int kBM = 64, kBN = 64, kThreads = 128;
+constexpr int kThreads = 320;
+constexpr int kRows = 128;              // query rows per softmax group / keys per tile
+constexpr int kSubBytes = 128 * 128;    // one 64-element-wide sub-tile: 128 rows x 128 bytes
 constexpr float kLog2e = 1.4426950408889634f;
 
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-  const int sz = valid ? 16 : 0;                      // src-size 0: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+struct PrefillParams {
+  int S, Hq, Hkv, causal;
+  float scale, softcap;
+  uint16_t* out;
+  long long out_ts;                     // elements between the output rows of consecutive tokens
+  uint32_t idesc_s, idesc_pv;
+  unsigned* status;                     // set to 1 if a bounded wait ran out (may be null)
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, uint32_t bar, int x, int y,
+                                            int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst_smem), "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+
+// Shared-memory descriptor of an MN-major operand stored as rows of 128 bytes (64 16-bit values of the
+// M/N dimension per row, one row per K index) with the 128-byte swizzle: the eight 16-byte units of a
+// row are contiguous, consecutive K rows are 128 bytes apart, groups of eight K rows `sbo` bytes apart
+// and consecutive 64-value chunks of the M/N dimension `lbo` bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16);
+  const uint32_t hi = (sbo >> 4) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
 }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (packed 16-bit pairs).
+__device__ __forceinline__ void mma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
-                                                  uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+
+// 32 lanes x 16 consecutive 32-bit columns, registers -> tensor memory.
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -43,181 +99,342 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b)
   }
 }
 
-// byte offset of 16-byte chunk `c` of row `r` in a [rows][D] 16-bit tile
-template <int D> __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4)); }
+template <int D> constexpr int kv_stages() { return D == 128 ? 2 : 4; }
+template <int D> constexpr int tile_bytes() { return (D / 64) * kSubBytes; }
+template <int D> constexpr int smem_bytes() { return 2 * tile_bytes<D>() + kv_stages<D>() * 2 * tile_bytes<D>() + 1024; }
 
-template <int D, int ROWS>
-__device__ __forceinline__ void load_tile(uint32_t dst_base, const uint16_t* src, int64_t row_stride, int row0,
-                                          int rows_total) {
-  constexpr int CH = D / 8;                            // chunks per row
-  static_assert(ROWS * CH % kThreads == 0, "tile does not divide among the threads");
+template <bool BF16, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, PrefillParams prm) {
+  constexpr int kSub = D / 64;
+  constexpr int kTile = tile_bytes<D>();
+  constexpr int kStages = kv_stages<D>();
+  constexpr uint32_t kColS = 0, kColO = 256;           // tensor-memory columns: S_w at 128 w, O_w at 256 + 128 w
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;                                  // [2][kTile]
+  uint8_t* sKV = base + 2 * kTile;                     // [kStages][K, V][kTile]
+  __shared__ __align__(8) uint64_t bar_q;
+  __shared__ __align__(8) uint64_t bar_kv_full[kStages];
+  __shared__ __align__(8) uint64_t bar_kv_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_s_full[2];      // S_w(j) complete (MMA commit)
+  __shared__ __align__(8) uint64_t bar_p_ready[2];     // P_w(j) written and O_w free (128 arrivals)
+  __shared__ __align__(8) uint64_t bar_o_full[2];      // O_w(j) complete (MMA commit)
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort = &abort_flag;
+
+  // heaviest query tiles first: with a causal mask the last rows see the most keys
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+  const int hkv = hq / (prm.Hq / prm.Hkv);
+  const int S = prm.S;
+  const int q0 = pair * 2 * kRows;
+  const int kv_tiles = (S + kRows - 1) / kRows;
+  int n_tiles[2];                                      // key tiles each query tile attends to
 #pragma unroll
-  for (int i = 0; i < ROWS * CH / kThreads; ++i) {
-    const int id = i * kThreads + threadIdx.x;
-    const int r = id / CH, c = id % CH;
-    const bool valid = row0 + r < rows_total;
-    const uint16_t* p = src + (int64_t)(valid ? row0 + r : 0) * row_stride + c * 8;
-    cp_async_16(dst_base + swz<D>(r, c), p, valid);
+  for (int w = 0; w < 2; ++w) {
+    const int qb = q0 + w * kRows;
+    n_tiles[w] = qb >= S ? 0 : (prm.causal ? min(qb / kRows + 1, kv_tiles) : kv_tiles);
   }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    tc::mbar_init(tc::smem_u32(&bar_q), 1);
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(tc::smem_u32(&bar_kv_full[s]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_kv_empty[s]), 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      tc::mbar_init(tc::smem_u32(&bar_s_full[w]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_p_ready[w]), kRows);
+      tc::mbar_init(tc::smem_u32(&bar_o_full[w]), 1);
+    }
+    tc::mbar_fence_init();
+    tc::tma_prefetch_descriptor(&tm_q);
+    tc::tma_prefetch_descriptor(&tm_k);
+    tc::tma_prefetch_descriptor(&tm_v);
+  }
+  if (warp == 9) {
+    tc::tmem_alloc(tc::smem_u32(&tmem_base_slot), 512);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 8) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int issued = 0;
+      const int nq = (n_tiles[0] > 0) + (n_tiles[1] > 0);
+      tc::mbar_arrive_expect_tx(tc::smem_u32(&bar_q), (uint32_t)(nq * kTile));
+      for (int w = 0; w < 2; ++w)
+        if (n_tiles[w] > 0)
+          for (int sub = 0; sub < kSub; ++sub)
+            tma_load_3d(tc::smem_u32(sQ + w * kTile + sub * kSubBytes), &tm_q, tc::smem_u32(&bar_q), hq * D + sub * 64,
+                        q0 + w * kRows, b);
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j % kStages;
+        const uint32_t ph = (uint32_t)(j / kStages) & 1u;
+        if (!tc::mbar_wait(tc::smem_u32(&bar_kv_empty[st]), ph ^ 1u, abort)) { ok = false; break; }
+        const uint32_t full = tc::smem_u32(&bar_kv_full[st]);
+        uint8_t* kt = sKV + st * 2 * kTile;
+        tc::mbar_arrive_expect_tx(full, 2 * kTile);
+        for (int sub = 0; sub < kSub; ++sub) {
+          tma_load_3d(tc::smem_u32(kt + sub * kSubBytes), &tm_k, full, hkv * D + sub * 64, j * kRows, b);
+          tma_load_3d(tc::smem_u32(kt + kTile + sub * kSubBytes), &tm_v, full, hkv * D + sub * 64, j * kRows, b);
+        }
+        ++issued;
+      }
+      if (!ok) {
+        // drain: wait (bounded) for the copies still in flight so that none lands after the block left
+        const uint64_t t0 = tc::global_timer_ns();
+        while (!tc::mbar_try_wait(tc::smem_u32(&bar_q), 0u) && tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
+        for (int i = max(0, issued - kStages); i < issued; ++i) {
+          const int st = i % kStages;
+          const uint32_t ph = (uint32_t)(i / kStages) & 1u;
+          while (!tc::mbar_try_wait(tc::smem_u32(&bar_kv_full[st]), ph) &&
+                 tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------- MMA issuer ---------------------------------
+    if (lane == 0 && n_max > 0) {
+      bool ok = tc::mbar_wait(tc::smem_u32(&bar_q), 0u, abort);
+      // S_w = Q_w K^T: both operands K-major; D / 16 instructions of K = 16
+      auto issue_s = [&](int w, int st) {
+        const uint32_t qa = tc::smem_u32(sQ + w * kTile), ka = tc::smem_u32(sKV + st * 2 * kTile);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (uint32_t)((ks / 4) * kSubBytes + (ks % 4) * 32);
+          tc::mma_ss<tc::MMA_F16>(tmem_base + kColS + (uint32_t)(w * 128), tc::smem_desc_k_major_sw128(qa + off),
+                                  tc::smem_desc_k_major_sw128(ka + off), prm.idesc_s, ks > 0 ? 1u : 0u);
+        }
+        tc::mma_commit(tc::smem_u32(&bar_s_full[w]));
+      };
+      // O_w = P_w V: P from tensor memory (8 packed columns per 16 keys), V MN-major (16 key rows per step)
+      auto issue_pv = [&](int w, int st) {
+        const uint32_t va = tc::smem_u32(sKV + st * 2 * kTile + kTile);
+#pragma unroll
+        for (int t = 0; t < kRows / 16; ++t)
+          mma_ts_f16(tmem_base + kColO + (uint32_t)(w * 128), tmem_base + kColS + (uint32_t)(w * 128 + t * 8),
+                     smem_desc_mn_major_sw128(va + (uint32_t)(t * 16 * 128), kSubBytes, 1024), prm.idesc_pv,
+                     t > 0 ? 1u : 0u);
+        tc::mma_commit(tc::smem_u32(&bar_o_full[w]));
+      };
+      if (ok) ok = tc::mbar_wait(tc::smem_u32(&bar_kv_full[0]), 0u, abort);
+      if (ok) {
+        tc::fence_after_sync();
+        for (int w = 0; w < 2; ++w)
+          if (n_tiles[w] > 0) issue_s(w, 0);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j % kStages, st1 = (j + 1) % kStages;
+        const uint32_t ph1 = (uint32_t)((j + 1) / kStages) & 1u;
+        for (int w = 0; w < 2 && ok; ++w) {
+          if (j >= n_tiles[w]) continue;
+          if (!tc::mbar_wait(tc::smem_u32(&bar_p_ready[w]), (uint32_t)j & 1u, abort)) { ok = false; break; }
+          tc::fence_after_sync();
+          issue_pv(w, st);
+          if (j + 1 < n_tiles[w]) {
+            if (!tc::mbar_wait(tc::smem_u32(&bar_kv_full[st1]), ph1, abort)) { ok = false; break; }
+            issue_s(w, st1);
+          }
+        }
+        if (ok) tc::mma_commit(tc::smem_u32(&bar_kv_empty[st]));       // K_j and V_j are free once these MMAs retire
+      }
+    }
+  } else {
+    // ------------------------------- softmax groups ------------------------------
+    const int w = warp >> 2;                           // query tile of this group
+    const int quad = warp & 3;                         // tensor-memory lane quadrant of this warp
+    const int r = quad * 32 + lane;                    // row of the tile handled by this thread
+    const int row = q0 + w * kRows + r;                // query position
+    const int n = n_tiles[w];
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_addr + kColS + (uint32_t)(w * 128);
+    const uint32_t t_o = tmem_base + lane_addr + kColO + (uint32_t)(w * 128);
+    const float sl = prm.scale * kLog2e;
+    const bool capped = prm.softcap != 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    bool ok = true;
+
+    // o = o * corr + O(tile) from tensor memory
+    auto accumulate_o = [&](float corr) {
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(t_o + (uint32_t)(c * 32), v);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(v[i]));
+      }
+    };
+
+    for (int j = 0; j < n; ++j) {
+      // every thread of the group must take the same path: OR the failure over the group's 128 threads
+      const bool failed = !tc::mbar_wait(tc::smem_u32(&bar_s_full[w]), (uint32_t)j & 1u, abort);
+      if (tc::named_barrier_or(1 + w, kRows, failed)) { ok = false; break; }
+      tc::fence_after_sync();
+      const int key0 = j * kRows;
+      // keys this row may see in this tile: [key0, key0 + limit)
+      int limit = S - key0;
+      if (prm.causal) limit = min(limit, row - key0 + 1);
+      const bool need_mask = limit < kRows;            // (limit >= 1 for every row < S: key 0 of the row's first tile)
+
+      // pass 1: row maximum of the (soft-capped) scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(t_s + (uint32_t)(c * 32), v);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(v[i]);
+          if (capped) x = prm.softcap * tanhf(x * prm.scale / prm.softcap) / prm.scale;
+          if (need_mask && c * 32 + i >= limit) x = -INFINITY;
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_safe = m_new == -INFINITY ? 0.f : m_new;           // a row without any visible key (row >= S)
+      const float corr = fast_exp2((m_run - m_safe) * sl);              // m_run = -inf: 0
+      m_run = m_new;
+      const float neg_ms = -m_safe * sl;
+
+      // pass 2: P = exp2(s * sl - m * sl), row sum, packed 16-bit pairs into the first half of S
+      float psum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(t_s + (uint32_t)(c * 32), v);
+        tc::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+          if (capped) {
+            x0 = prm.softcap * tanhf(x0 * prm.scale / prm.softcap) / prm.scale;
+            x1 = prm.softcap * tanhf(x1 * prm.scale / prm.softcap) / prm.scale;
+          }
+          float p0 = fast_exp2(fmaf(x0, sl, neg_ms)), p1 = fast_exp2(fmaf(x1, sl, neg_ms));
+          if (need_mask) {
+            if (c * 32 + i >= limit) p0 = 0.f;
+            if (c * 32 + i + 1 >= limit) p1 = 0.f;
+          }
+          pk[i / 2] = pack2<BF16>(p0, p1);
+          // the sum uses the rounded values the tensor core will multiply
+          if constexpr (BF16) {
+            psum += __uint_as_float(pk[i / 2] << 16) + __uint_as_float(pk[i / 2] & 0xffff0000u);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&pk[i / 2]);
+            psum += __low2float(h) + __high2float(h);
+          }
+        }
+        tmem_st_32x16(t_s + (uint32_t)(c * 16), pk);
+      }
+      l_run = fmaf(l_run, corr, psum);
+      tmem_st_wait();
+
+      // O of the previous key tile: it must be out of tensor memory before P_j V_j may overwrite it
+      if (j > 0) {
+        const bool f2 = !tc::mbar_wait(tc::smem_u32(&bar_o_full[w]), (uint32_t)(j - 1) & 1u, abort);
+        if (tc::named_barrier_or(1 + w, kRows, f2)) { ok = false; break; }
+        tc::fence_after_sync();
+        accumulate_o(corr_prev);
+      }
+      corr_prev = corr;
+      tc::fence_before_sync();
+      tc::mbar_arrive(tc::smem_u32(&bar_p_ready[w]));
+    }
+
+    if (ok && n > 0) {
+      const bool f3 = !tc::mbar_wait(tc::smem_u32(&bar_o_full[w]), (uint32_t)(n - 1) & 1u, abort);
+      if (!tc::named_barrier_or(1 + w, kRows, f3)) {
+        tc::fence_after_sync();
+        accumulate_o(corr_prev);
+        if (row < S) {
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          uint4* dst = reinterpret_cast<uint4*>(prm.out + ((long long)b * S + row) * prm.out_ts + (long long)hq * D);
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i)
+            dst[i] = make_uint4(pack2<BF16>(o[8 * i] * inv, o[8 * i + 1] * inv),
+                                pack2<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
+                                pack2<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv),
+                                pack2<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown ---------------------------------------
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && abort_flag && prm.status) *prm.status = 1u;
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [B, S, H * d] 16-bit tensor with `ts` elements between tokens; box = 64 elements x 128 tokens of one
+// sequence (tokens beyond S read as zero, never the next sequence's).
+int make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t S, int64_t width, int64_t ts) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)(ts * 2), (cuuint64_t)(S * ts * 2)};
+  cuuint32_t box[3] = {64, (cuuint32_t)kRows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LLMQRT_OK;
 }
 
 template <bool BF16, int D>
-__global__ void __launch_bounds__(kThreads)
-attn_prefill_kernel(const uint16_t* __restrict__ q, int64_t q_ts, const uint16_t* __restrict__ k,
-                    const uint16_t* __restrict__ v, int64_t kv_ts, uint16_t* __restrict__ out, int64_t out_ts, int S,
-                    int Hq, int Hkv, int causal, float scale, float softcap) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kTileBytes = kBN * D * 2;
-  const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem);
-  const uint32_t sK = sQ + kBM * D * 2, sV = sK + 2 * kTileBytes;
-
-  const int qt = gridDim.x - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
-  const int hkv = hq / (Hq / Hkv);
-  const int q0 = qt * kBM;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-
-  const uint16_t* qb = q + (int64_t)b * S * q_ts + (int64_t)hq * D;
-  const uint16_t* kb = k + (int64_t)b * S * kv_ts + (int64_t)hkv * D;
-  const uint16_t* vb = v + (int64_t)b * S * kv_ts + (int64_t)hkv * D;
-
-  const int n_tiles = causal ? min((q0 + kBM + kBN - 1) / kBN, (S + kBN - 1) / kBN) : (S + kBN - 1) / kBN;
-
-  load_tile<D, kBM>(sQ, qb, q_ts, q0, S);
-  load_tile<D, kBN>(sK, kb, kv_ts, 0, S);
-  load_tile<D, kBN>(sV, vb, kv_ts, 0, S);
-  cp_async_commit();
-
-  uint32_t qf[D / 16][4];
-  float o[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  const float sl2 = scale * kLog2e;
-
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int buf = tile & 1;
-    if (tile + 1 < n_tiles) {                           // prefetch the next K/V tile into the other buffer
-      load_tile<D, kBN>(sK + (buf ^ 1) * kTileBytes, kb, kv_ts, (tile + 1) * kBN, S);
-      load_tile<D, kBN>(sV + (buf ^ 1) * kTileBytes, vb, kv_ts, (tile + 1) * kBN, S);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-
-    if (tile == 0) {
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const int r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), c = 2 * ks + (lane >> 4);
-        ldmatrix_x4(sQ + swz<D>(r, c), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
-      }
-    }
-
-    // A key tile entirely above this warp's 16 rows is masked out completely: nothing to compute
-    // (the barriers below are still reached by every warp).
-    const bool skip = causal && tile * kBN > q0 + warp * 16 + 15;
-    if (!skip) {
-    // ---- S = Q K^T (16 x 64 per warp) ----
-    float s[kBN / 8][4];
-#pragma unroll
-    for (int nb = 0; nb < kBN / 8; ++nb) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) s[nb][c] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ks += 2) {
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(sK + buf * kTileBytes + swz<D>(nb * 8 + (lane & 7), 2 * ks + (lane >> 3)), b0, b1, b2, b3);
-        mma_16816<BF16>(s[nb], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-        mma_16816<BF16>(s[nb], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], b2, b3);
-      }
-    }
-
-    // ---- scale, mask, online softmax (rows g and g+8 of this warp's 16) ----
-    const int key_base = tile * kBN;
-    const bool need_mask = (key_base + kBN > S) || (causal && key_base + kBN > q0 + warp * 16);
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nb = 0; nb < kBN / 8; ++nb)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float x = s[nb][c];
-        if (softcap != 0.f) x = softcap * tanhf(x * scale / softcap) * kLog2e;
-        else x *= sl2;
-        if (need_mask) {
-          const int key = key_base + nb * 8 + 2 * t + (c & 1);
-          const int row = q0 + warp * 16 + g + 8 * (c >> 1);
-          if (key >= S || (causal && key > row)) x = -INFINITY;
-        }
-        s[nb][c] = x;
-        mx[c >> 1] = fmaxf(mx[c >> 1], x);
-      }
-    float corr[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m_run[r], mx[r]);
-      // a fully masked row keeps m = -inf; use 0 as the reference point so that exp2 yields 0, not NaN
-      const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-      corr[r] = exp2f(m_run[r] - m_safe);
-      m_run[r] = m_new;
-      mx[r] = m_safe;
-    }
-    float psum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int nb = 0; nb < kBN / 8; ++nb)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float p = exp2f(s[nb][c] - mx[c >> 1]);
-        s[nb][c] = p;
-        psum[c >> 1] += p;
-      }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + psum[r];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0];
-      o[i][2] *= corr[1]; o[i][3] *= corr[1];
-    }
-
-    // ---- O += P V ----
-#pragma unroll
-    for (int kk = 0; kk < kBN / 16; ++kk) {
-      const uint32_t a0 = pack2<BF16>(s[2 * kk][0], s[2 * kk][1]);
-      const uint32_t a1 = pack2<BF16>(s[2 * kk][2], s[2 * kk][3]);
-      const uint32_t a2 = pack2<BF16>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      const uint32_t a3 = pack2<BF16>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-      for (int db = 0; db < D / 8; db += 2) {
-        uint32_t b0, b1, b2, b3;
-        const int r = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), c = db + (lane >> 4);
-        ldmatrix_x4_trans(sV + buf * kTileBytes + swz<D>(r, c), b0, b1, b2, b3);
-        mma_16816<BF16>(o[db], a0, a1, a2, a3, b0, b1);
-        mma_16816<BF16>(o[db + 1], a0, a1, a2, a3, b2, b3);
-      }
-    }
-    }
-    __syncthreads();                                    // everyone is done with `buf` before it is refilled
-  }
-
-  // ---- normalise and store ----
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-  }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = q0 + warp * 16 + g + 8 * r;
-    if (row >= S) continue;
-    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
-    uint32_t* dst = reinterpret_cast<uint32_t*>(out + ((int64_t)b * S + row) * out_ts + (int64_t)hq * D);
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) dst[i * 4 + t] = pack2<BF16>(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
-  }
+int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, PrefillParams prm, int64_t B,
+                   cudaStream_t st) {
+  auto kern = attn_prefill_tc_kernel<BF16, D>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<D>())) return rc;
+  const uint32_t fmt = BF16 ? 1u : 0u;
+  prm.idesc_s = tc::instr_desc(1, fmt, fmt, kRows, kRows);
+  prm.idesc_pv = tc::instr_desc(1, fmt, fmt, kRows, D) | (1u << 16);       // bit 16: B operand is MN-major
+  const dim3 grid((unsigned)ceil_div(prm.S, 2 * kRows), (unsigned)prm.Hq, (unsigned)B);
+  kern<<<grid, kThreads, smem_bytes<D>(), st>>>(tq, tk, tv, prm);
+  return check_launch("attn_prefill");
 }
 
 }  // namespace
@@ -233,28 +450,26 @@ extern "C" int llmqrt_attn_prefill(const void* q, int64_t q_token_stride, const 
   LLMQRT_REQUIRE(d == 64 || d == 128, "attn_prefill: head_dim must be 64 or 128 (got %lld)", (long long)d);
   LLMQRT_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq < 65536 && B < 65536 && B >= 0 && S >= 0 && S < (1 << 30),
                  "attn_prefill: bad shape");
-  LLMQRT_REQUIRE(q_token_stride % 8 == 0 && kv_token_stride % 8 == 0 && out_token_stride % 2 == 0,
-                 "attn_prefill: token strides must be multiples of 8 elements");
+  LLMQRT_REQUIRE(q_token_stride % 8 == 0 && kv_token_stride % 8 == 0 && out_token_stride % 8 == 0 &&
+                 q_token_stride >= Hq * d && kv_token_stride >= Hkv * d && out_token_stride >= Hq * d,
+                 "attn_prefill: token strides must cover a token and be multiples of 8 elements");
   if (B == 0 || S == 0) return LLMQRT_OK;
   LLMQRT_REQUIRE(q && k && v && out, "attn_prefill: null pointer");
-  LLMQRT_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
-                 (reinterpret_cast<uintptr_t>(out) & 3) == 0, "attn_prefill: pointers must be 16-byte aligned");
+  LLMQRT_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                   reinterpret_cast<uintptr_t>(out)) & 15) == 0, "attn_prefill: pointers must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  const dim3 grid((unsigned)ceil_div(S, kBM), (unsigned)Hq, (unsigned)B);
-  const float scale = 1.0f / sqrtf((float)d);
-  const int smem = (kBM + 4 * kBN) * (int)d * 2;
-#define LLMQRT_RUN(BF, DD)                                                                                         \
-  do {                                                                                                             \
-    auto kern = attn_prefill_kernel<BF, DD>;                                                                       \
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;                \
-    kern<<<grid, kThreads, smem, st>>>(reinterpret_cast<const uint16_t*>(q), q_token_stride,                       \
-                                       reinterpret_cast<const uint16_t*>(k), reinterpret_cast<const uint16_t*>(v), \
-                                       kv_token_stride, reinterpret_cast<uint16_t*>(out), out_token_stride, (int)S, \
-                                       (int)Hq, (int)Hkv, causal, scale, softcap);                                  \
-  } while (0)
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_token_map(&tq, q, B, S, Hq * d, q_token_stride)) return rc;
+  if (int rc = make_token_map(&tk, k, B, S, Hkv * d, kv_token_stride)) return rc;
+  if (int rc = make_token_map(&tv, v, B, S, Hkv * d, kv_token_stride)) return rc;
+  PrefillParams prm{};
+  prm.S = (int)S; prm.Hq = (int)Hq; prm.Hkv = (int)Hkv; prm.causal = causal;
+  prm.scale = 1.0f / sqrtf((float)d);
+  prm.softcap = softcap;
+  prm.out = reinterpret_cast<uint16_t*>(out);
+  prm.out_ts = out_token_stride;
+  prm.status = nullptr;
   const bool bf = dtype == LLMQRT_BF16;
-  if (d == 128) { if (bf) LLMQRT_RUN(true, 128); else LLMQRT_RUN(false, 128); }
-  else { if (bf) LLMQRT_RUN(true, 64); else LLMQRT_RUN(false, 64); }
-#undef LLMQRT_RUN
-  return check_launch("attn_prefill");
+  if (d == 128) return bf ? launch_prefill<true, 128>(tq, tk, tv, prm, B, st) : launch_prefill<false, 128>(tq, tk, tv, prm, B, st);
+  return bf ? launch_prefill<true, 64>(tq, tk, tv, prm, B, st) : launch_prefill<false, 64>(tq, tk, tv, prm, B, st);
 }
