@@ -1,26 +1,32 @@
 // Prefill attention over the new tokens on the 5th-generation tensor cores:
 //     O = softmax(mask(Q K^T / sqrt(d))) V,  causal or not, GQA (query head h reads KV head h / (Hq/Hkv)).
 //
-// One CTA owns 256 consecutive query rows of one head as two 128-row tiles.  Roles (320 threads):
+// One CTA owns 256 consecutive query rows of one head as two 128-row tiles.  Roles (384 threads):
 //   warps 0-3 / 4-7  one softmax group per query tile, one thread per query row;
 //   warp 8           TMA producer: the two Q tiles once, then K and V tiles of 128 keys through a ring;
-//   warp 9           owns tensor memory; its lane 0 issues every tcgen05.mma.
+//   warp 9           owns tensor memory; its lane 0 issues every tcgen05.mma;
+//   warps 10-11      none: they complete the third warpgroup, which hands most of its registers to
+//                    the softmax groups (setmaxnreg), whose threads hold a whole 128-wide row of S.
 // Per key tile j and query tile w:
 //   S_w = Q_w K_j^T    tcgen05.mma kind::f16, both operands K-major in shared memory (TMA, 128-byte
 //                      swizzle), 128 x 128 fp32 accumulator in tensor memory;
-//   softmax            the row's thread reads S with tcgen05.ld (two passes: maximum, then exponentials),
-//                      keeps the running maximum and sum in registers and writes P as packed 16-bit
-//                      pairs back into tensor memory over the first half of S (tcgen05.st);
-//   O_j = P V_j        tcgen05.mma with P as the tensor-memory operand and V as an MN-major
-//                      shared-memory operand (V tiles are stored [key][d], d contiguous); a fresh
-//                      128 x d accumulator per key tile.
-// The row's thread adds O_j into its register accumulator, o = o * exp2(m_old - m_new) + O_j, so the
-// accumulator in tensor memory never has to be rescaled.  The tensor pipe alternates between the two
-// query tiles: while one group runs its softmax, the pipe multiplies for the other.
+//   softmax            the row's thread reads the whole S row with tcgen05.ld, keeps the reference
+//                      maximum and the sum in registers and writes P as packed 16-bit pairs back into
+//                      tensor memory over the first half of S (tcgen05.st);
+//   O_w += P V_j       tcgen05.mma with P as the tensor-memory operand and V as an MN-major
+//                      shared-memory operand (V tiles are stored [key][d], d contiguous), accumulating
+//                      over the key tiles in a 128 x d fp32 accumulator in tensor memory.
+// The exponentials of a row are taken relative to a reference maximum that is only moved when the
+// row's true maximum has grown by more than 2^8 since (P then stays below 256, exact enough in 16
+// bits and far from overflow): moving it means scaling the row of O in tensor memory (a tcgen05.ld /
+// tcgen05.st round trip), which with this rule happens in the first tiles of a row and hardly ever
+// afterwards.  The tensor pipe alternates between the two query tiles: while one group runs its
+// softmax, the pipe multiplies for the other.
 //
 // Tensor memory (512 columns): S_0 | S_1 | O_0 | O_1, 128 columns each (O uses d).  P_w aliases the
 // first 64 columns of S_w; the MMAs of one CTA execute in issue order, and S_w(j+1) is only issued
-// after P_w(j) V_j, so the alias is never overwritten while it is being read.
+// after P_w(j) V_j, so the alias is never overwritten while it is being read, and S_w(j+1) complete
+// implies P_w(j) V_j complete, so O_w is at rest whenever its group touches it.
 //
 // Every wait on an mbarrier is bounded; when one runs out the block raises a flag, every role
 // leaves its loop, outstanding copies are drained, tensor memory is freed and a status word is set.
@@ -32,7 +38,7 @@
 namespace llmqrt {
 namespace {
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
 constexpr int kRows = 128;              // query rows per softmax group / keys per tile
 constexpr int kSubBytes = 128 * 128;    // one 64-element-wide sub-tile: 128 rows x 128 bytes
 constexpr float kLog2e = 1.4426950408889634f;
@@ -81,6 +87,17 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -120,8 +137,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   __shared__ __align__(8) uint64_t bar_kv_full[kStages];
   __shared__ __align__(8) uint64_t bar_kv_empty[kStages];
   __shared__ __align__(8) uint64_t bar_s_full[2];      // S_w(j) complete (MMA commit)
-  __shared__ __align__(8) uint64_t bar_p_ready[2];     // P_w(j) written and O_w free (128 arrivals)
-  __shared__ __align__(8) uint64_t bar_o_full[2];      // O_w(j) complete (MMA commit)
+  __shared__ __align__(8) uint64_t bar_p_ready[2];     // P_w(j) written, O_w rescaled if need be (128 arrivals)
+  __shared__ __align__(8) uint64_t bar_o_full[2];      // O_w complete after the last key tile (MMA commit)
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -168,6 +185,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
 
+  // Register budget per warpgroup (8 x 216 + 4 x 72 registers per lane fit the SM's file): each role
+  // branch starts by shrinking or growing its warpgroup's share.
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 8) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
@@ -221,14 +242,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc::mma_commit(tc::smem_u32(&bar_s_full[w]));
       };
       // O_w = P_w V: P from tensor memory (8 packed columns per 16 keys), V MN-major (16 key rows per step)
-      auto issue_pv = [&](int w, int st) {
+      auto issue_pv = [&](int w, int st, int j) {
         const uint32_t va = tc::smem_u32(sKV + st * 2 * kTile + kTile);
 #pragma unroll
         for (int t = 0; t < kRows / 16; ++t)
           mma_ts_f16(tmem_base + kColO + (uint32_t)(w * 128), tmem_base + kColS + (uint32_t)(w * 128 + t * 8),
                      smem_desc_mn_major_sw128(va + (uint32_t)(t * 16 * 128), kSubBytes, 1024), prm.idesc_pv,
-                     t > 0 ? 1u : 0u);
-        tc::mma_commit(tc::smem_u32(&bar_o_full[w]));
+                     (j > 0 || t > 0) ? 1u : 0u);
+        if (j == n_tiles[w] - 1) tc::mma_commit(tc::smem_u32(&bar_o_full[w]));        // the row's last tile: O complete
       };
       if (ok) ok = tc::mbar_wait(tc::smem_u32(&bar_kv_full[0]), 0u, abort);
       if (ok) {
@@ -243,7 +264,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           if (j >= n_tiles[w]) continue;
           if (!tc::mbar_wait(tc::smem_u32(&bar_p_ready[w]), (uint32_t)j & 1u, abort)) { ok = false; break; }
           tc::fence_after_sync();
-          issue_pv(w, st);
+          issue_pv(w, st, j);
           if (j + 1 < n_tiles[w]) {
             if (!tc::mbar_wait(tc::smem_u32(&bar_kv_full[st1]), ph1, abort)) { ok = false; break; }
             issue_s(w, st1);
@@ -252,8 +273,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (ok) tc::mma_commit(tc::smem_u32(&bar_kv_empty[st]));       // K_j and V_j are free once these MMAs retire
       }
     }
+  }
   } else {
     // ------------------------------- softmax groups ------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int w = warp >> 2;                           // query tile of this group
     const int quad = warp & 3;                         // tensor-memory lane quadrant of this warp
     const int r = quad * 32 + lane;                    // row of the tile handled by this thread
@@ -264,23 +287,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const uint32_t t_o = tmem_base + lane_addr + kColO + (uint32_t)(w * 128);
     const float sl = prm.scale * kLog2e;
     const bool capped = prm.softcap != 0.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    float m_ref = -INFINITY, l_run = 0.f;              // reference maximum of the exponentials, running sum
     bool ok = true;
-
-    // o = o * corr + O(tile) from tensor memory
-    auto accumulate_o = [&](float corr) {
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(t_o + (uint32_t)(c * 32), v);
-        tc::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(v[i]));
-      }
-    };
 
     for (int j = 0; j < n; ++j) {
       // every thread of the group must take the same path: OR the failure over the group's 128 threads
@@ -293,87 +301,88 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (prm.causal) limit = min(limit, row - key0 + 1);
       const bool need_mask = limit < kRows;            // (limit >= 1 for every row < S: key 0 of the row's first tile)
 
-      // pass 1: row maximum of the (soft-capped) scores
+      // the whole row of S: four loads in flight, one wait
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(t_s + (uint32_t)(c * 32), v[c]);
+      tc::tmem_ld_wait();
+
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(t_s + (uint32_t)(c * 32), v);
-        tc::tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
+          float x = __uint_as_float(v[c][i]);
           if (capped) x = prm.softcap * tanhf(x * prm.scale / prm.softcap) / prm.scale;
           if (need_mask && c * 32 + i >= limit) x = -INFINITY;
+          v[c][i] = __float_as_uint(x);
           mx = fmaxf(mx, x);
         }
+      // Move the reference only when the maximum has outgrown it by more than 2^8 (always on the first
+      // tile).  tcgen05.ld / st are warp-wide, so the decision is taken per warp; a lane of a moving warp
+      // moves to its own exact maximum.
+      const bool grow = (mx - m_ref) * sl > 8.f;       // m_ref = -inf: true unless the row sees no key at all
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = fast_exp2((m_ref - m_safe) * sl);            // m_ref = -inf: 0
+        m_ref = m_new;
+        l_run *= corr;
+        if (j > 0) {                                    // O holds the tiles before this one: scale its row
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            tc::tmem_ld_32x32(t_o + (uint32_t)(c * 32), ov);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+            tmem_st_32x32(t_o + (uint32_t)(c * 32), ov);
+          }
+        }
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_safe = m_new == -INFINITY ? 0.f : m_new;           // a row without any visible key (row >= S)
-      const float corr = fast_exp2((m_run - m_safe) * sl);              // m_run = -inf: 0
-      m_run = m_new;
-      const float neg_ms = -m_safe * sl;
+      const float neg_ms = m_ref == -INFINITY ? 0.f : -m_ref * sl;
 
-      // pass 2: P = exp2(s * sl - m * sl), row sum, packed 16-bit pairs into the first half of S
-      float psum = 0.f;
-#pragma unroll 1
+      // P = exp2(s * sl - m * sl), row sum, packed 16-bit pairs into the first half of S
+      float psum0 = 0.f, psum1 = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(t_s + (uint32_t)(c * 32), v);
-        tc::tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
-          if (capped) {
-            x0 = prm.softcap * tanhf(x0 * prm.scale / prm.softcap) / prm.scale;
-            x1 = prm.softcap * tanhf(x1 * prm.scale / prm.softcap) / prm.scale;
-          }
-          float p0 = fast_exp2(fmaf(x0, sl, neg_ms)), p1 = fast_exp2(fmaf(x1, sl, neg_ms));
-          if (need_mask) {
-            if (c * 32 + i >= limit) p0 = 0.f;
-            if (c * 32 + i + 1 >= limit) p1 = 0.f;
-          }
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[c][i]), sl, neg_ms));       // masked: exp2(-inf) = 0
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[c][i + 1]), sl, neg_ms));
+          psum0 += p0;
+          psum1 += p1;
           pk[i / 2] = pack2<BF16>(p0, p1);
-          // the sum uses the rounded values the tensor core will multiply
-          if constexpr (BF16) {
-            psum += __uint_as_float(pk[i / 2] << 16) + __uint_as_float(pk[i / 2] & 0xffff0000u);
-          } else {
-            const __half2 h = *reinterpret_cast<const __half2*>(&pk[i / 2]);
-            psum += __low2float(h) + __high2float(h);
-          }
         }
         tmem_st_32x16(t_s + (uint32_t)(c * 16), pk);
       }
-      l_run = fmaf(l_run, corr, psum);
+      l_run += psum0 + psum1;
       tmem_st_wait();
-
-      // O of the previous key tile: it must be out of tensor memory before P_j V_j may overwrite it
-      if (j > 0) {
-        const bool f2 = !tc::mbar_wait(tc::smem_u32(&bar_o_full[w]), (uint32_t)(j - 1) & 1u, abort);
-        if (tc::named_barrier_or(1 + w, kRows, f2)) { ok = false; break; }
-        tc::fence_after_sync();
-        accumulate_o(corr_prev);
-      }
-      corr_prev = corr;
       tc::fence_before_sync();
       tc::mbar_arrive(tc::smem_u32(&bar_p_ready[w]));
     }
 
     if (ok && n > 0) {
-      const bool f3 = !tc::mbar_wait(tc::smem_u32(&bar_o_full[w]), (uint32_t)(n - 1) & 1u, abort);
+      const bool f3 = !tc::mbar_wait(tc::smem_u32(&bar_o_full[w]), 0u, abort);
       if (!tc::named_barrier_or(1 + w, kRows, f3)) {
         tc::fence_after_sync();
-        accumulate_o(corr_prev);
-        if (row < S) {
-          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-          uint4* dst = reinterpret_cast<uint4*>(prm.out + ((long long)b * S + row) * prm.out_ts + (long long)hq * D);
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint4* dst = reinterpret_cast<uint4*>(prm.out + ((long long)b * S + row) * prm.out_ts + (long long)hq * D);
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i)
-            dst[i] = make_uint4(pack2<BF16>(o[8 * i] * inv, o[8 * i + 1] * inv),
-                                pack2<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
-                                pack2<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv),
-                                pack2<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ov[32];
+          tc::tmem_ld_32x32(t_o + (uint32_t)(c * 32), ov);
+          tc::tmem_ld_wait();
+          if (row < S) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[c * 4 + i] = make_uint4(
+                  pack2<BF16>(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv),
+                  pack2<BF16>(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv),
+                  pack2<BF16>(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv),
+                  pack2<BF16>(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv));
+          }
         }
       }
     }
