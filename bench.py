@@ -51,8 +51,12 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=28, help="decoder layers (28 = Qwen2-7B; fewer is NOT the benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", nargs="?", const="int8,fp8,awq,attn", default=None,
-                    help="time every operator shape of the other configurations against its bound instead")
+                    help="time every operator shape of the other configurations against its bound instead "
+                         "(comma list of int8, fp8, awq, attn, attn_decode, attn_prefill)")
     ap.add_argument("--reps", type=int, default=20, help="graph replays per shape of --sweep")
+    ap.add_argument("--no-pipe-peaks", action="store_true",
+                    help="--sweep: skip the library GEMMs that measure the tensor-pipe rates (use the recorded bf16 "
+                         "rate and twice that for the 8-bit kinds); keeps a profiler run short")
     return ap.parse_args()
 
 
@@ -487,7 +491,13 @@ def run_sweep(args):
     dev = torch.device("cuda")
     hbm_gbs, peak_kind = measured_peak_hbm()
     hbm = hbm_gbs * 1e9
-    pipes = measure_pipe_peaks(torch)
+    pipes = measure_pipe_peaks(torch) if not args.no_pipe_peaks else {"bf16": None, "fp8": None, "int8": None}
+    if pipes["bf16"] is None:                           # not measured here: the pool's recorded cuBLAS bf16 rate
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                pipes["bf16"] = float(json.load(f)["bf16_tflops"]) * 1e12
+        except Exception:
+            pipes["bf16"] = 1590e12
     pipe16 = pipes["bf16"]
     pipe_f8 = pipes["fp8"] or 2 * pipe16
     pipe_i8 = pipes["int8"] or 2 * pipe16
@@ -560,9 +570,10 @@ def run_sweep(args):
                 x = torch.randn(M, K, generator=g, device=dev).half()
                 secs = _time_graph(torch, lambda: [ops.awq_gemm(x, p) for p in layers], reps) / n
                 report(tag, M, N, K, secs, 2 * M * K + wbytes + 2 * M * N, 2 * M * N * K, pipe16)
-    if "attn" in what:
+    Hq, Hkv, d = 28, 4, 128
+    if "attn" in what or "attn_decode" in what:
         g = torch.Generator(device=dev).manual_seed(3)
-        B, Hq, Hkv, d, Smax = 32, 28, 4, 128, 8192
+        B, Smax = 32, 8192
         lens = torch.randint(512, 8193, (B,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
         kc = torch.randn(B, Smax, Hkv, d, generator=g, device=dev, dtype=torch.float16)     # 268 MB each: beyond L2
         vc = torch.randn(B, Smax, Hkv, d, generator=g, device=dev, dtype=torch.float16)
@@ -573,6 +584,8 @@ def run_sweep(args):
         report("attn decode b32 ctx U[512,8192]", B, ctx // B, d, secs, ctx * Hkv * d * 2 * 2 + 2 * B * Hq * d * 2,
                4 * ctx * Hq * d, pipe16)
         del kc, vc
+    if "attn" in what or "attn_prefill" in what:
+        g = torch.Generator(device=dev).manual_seed(4)
         Bp, S = 4, 2048
         qs = [torch.randn(Bp, S, Hq, d, generator=g, device=dev, dtype=torch.float16) for _ in range(2)]
         ks = [torch.randn(Bp, S, Hkv, d, generator=g, device=dev, dtype=torch.float16) for _ in range(2)]

@@ -4,7 +4,7 @@
 // One CTA owns 256 consecutive query rows of one head as two 128-row tiles.  Roles (384 threads):
 //   warps 0-3 / 4-7  one softmax group per query tile, one thread per query row;
 //   warp 8           TMA producer: the two Q tiles once, then K and V tiles of 128 keys through a ring;
-//   warp 9           owns tensor memory; its lane 0 issues every tcgen05.mma;
+//   warp 9           owns tensor memory and issues every tcgen05.mma (one elected lane, warp-uniform loop);
 //   warps 10-11      none: they complete the third warpgroup, which hands most of its registers to
 //                    the softmax groups (setmaxnreg), whose threads hold a whole 128-wide row of S.
 // Per key tile j and query tile w:
@@ -87,15 +87,12 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -116,9 +113,13 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b)
   }
 }
 
-template <int D> constexpr int kv_stages() { return D == 128 ? 2 : 4; }
+// K and V tiles travel through rings of their own: a K tile is free as soon as both S products that
+// read it have retired, long before the V tile of the same keys, so its slot can be refilled a whole
+// key tile earlier.  With 128-wide heads shared memory holds two Q tiles, three K and two V tiles.
+template <int D> constexpr int k_stages() { return D == 128 ? 3 : 4; }
+template <int D> constexpr int v_stages() { return D == 128 ? 2 : 4; }
 template <int D> constexpr int tile_bytes() { return (D / 64) * kSubBytes; }
-template <int D> constexpr int smem_bytes() { return 2 * tile_bytes<D>() + kv_stages<D>() * 2 * tile_bytes<D>() + 1024; }
+template <int D> constexpr int smem_bytes() { return (2 + k_stages<D>() + v_stages<D>()) * tile_bytes<D>() + 1024; }
 
 template <bool BF16, int D>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -126,16 +127,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const __grid_constant__ CUtensorMap tm_v, PrefillParams prm) {
   constexpr int kSub = D / 64;
   constexpr int kTile = tile_bytes<D>();
-  constexpr int kStages = kv_stages<D>();
+  constexpr int kKS = k_stages<D>(), kVS = v_stages<D>();
   constexpr uint32_t kColS = 0, kColO = 256;           // tensor-memory columns: S_w at 128 w, O_w at 256 + 128 w
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = base;                                  // [2][kTile]
-  uint8_t* sKV = base + 2 * kTile;                     // [kStages][K, V][kTile]
+  uint8_t* sK = base + 2 * kTile;                      // [kKS][kTile]
+  uint8_t* sV = sK + kKS * kTile;                      // [kVS][kTile]
   __shared__ __align__(8) uint64_t bar_q;
-  __shared__ __align__(8) uint64_t bar_kv_full[kStages];
-  __shared__ __align__(8) uint64_t bar_kv_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_k_full[kKS];
+  __shared__ __align__(8) uint64_t bar_k_empty[kKS];
+  __shared__ __align__(8) uint64_t bar_v_full[kVS];
+  __shared__ __align__(8) uint64_t bar_v_empty[kVS];
   __shared__ __align__(8) uint64_t bar_s_full[2];      // S_w(j) complete (MMA commit)
   __shared__ __align__(8) uint64_t bar_p_ready[2];     // P_w(j) written, O_w rescaled if need be (128 arrivals)
   __shared__ __align__(8) uint64_t bar_o_full[2];      // O_w complete after the last key tile (MMA commit)
@@ -162,9 +166,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (threadIdx.x == 0) {
     abort_flag = 0;
     tc::mbar_init(tc::smem_u32(&bar_q), 1);
-    for (int s = 0; s < kStages; ++s) {
-      tc::mbar_init(tc::smem_u32(&bar_kv_full[s]), 1);
-      tc::mbar_init(tc::smem_u32(&bar_kv_empty[s]), 1);
+    for (int s = 0; s < kKS; ++s) {
+      tc::mbar_init(tc::smem_u32(&bar_k_full[s]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_k_empty[s]), 1);
+    }
+    for (int s = 0; s < kVS; ++s) {
+      tc::mbar_init(tc::smem_u32(&bar_v_full[s]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_v_empty[s]), 1);
     }
     for (int w = 0; w < 2; ++w) {
       tc::mbar_init(tc::smem_u32(&bar_s_full[w]), 1);
@@ -192,7 +200,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (warp == 8) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
-      int issued = 0;
       const int nq = (n_tiles[0] > 0) + (n_tiles[1] > 0);
       tc::mbar_arrive_expect_tx(tc::smem_u32(&bar_q), (uint32_t)(nq * kTile));
       for (int w = 0; w < 2; ++w)
@@ -201,76 +208,95 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             tma_load_3d(tc::smem_u32(sQ + w * kTile + sub * kSubBytes), &tm_q, tc::smem_u32(&bar_q), hq * D + sub * 64,
                         q0 + w * kRows, b);
       bool ok = true;
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (uint32_t)(j / kStages) & 1u;
-        if (!tc::mbar_wait(tc::smem_u32(&bar_kv_empty[st]), ph ^ 1u, abort)) { ok = false; break; }
-        const uint32_t full = tc::smem_u32(&bar_kv_full[st]);
-        uint8_t* kt = sKV + st * 2 * kTile;
-        tc::mbar_arrive_expect_tx(full, 2 * kTile);
-        for (int sub = 0; sub < kSub; ++sub) {
-          tma_load_3d(tc::smem_u32(kt + sub * kSubBytes), &tm_k, full, hkv * D + sub * 64, j * kRows, b);
-          tma_load_3d(tc::smem_u32(kt + kTile + sub * kSubBytes), &tm_v, full, hkv * D + sub * 64, j * kRows, b);
+      // K runs up to two tiles ahead of V (its ring is deeper and its slots come free earlier)
+      int kj = 0, vj = 0;
+      while (ok && (kj < n_max || vj < n_max)) {
+        if (kj < n_max && (kj <= vj + 2 || vj >= n_max)) {
+          const int st = kj % kKS;
+          const uint32_t ph = (uint32_t)(kj / kKS) & 1u;
+          if (!tc::mbar_wait(tc::smem_u32(&bar_k_empty[st]), ph ^ 1u, abort)) { ok = false; break; }
+          const uint32_t full = tc::smem_u32(&bar_k_full[st]);
+          tc::mbar_arrive_expect_tx(full, kTile);
+          for (int sub = 0; sub < kSub; ++sub)
+            tma_load_3d(tc::smem_u32(sK + st * kTile + sub * kSubBytes), &tm_k, full, hkv * D + sub * 64, kj * kRows, b);
+          ++kj;
+        } else {
+          const int st = vj % kVS;
+          const uint32_t ph = (uint32_t)(vj / kVS) & 1u;
+          if (!tc::mbar_wait(tc::smem_u32(&bar_v_empty[st]), ph ^ 1u, abort)) { ok = false; break; }
+          const uint32_t full = tc::smem_u32(&bar_v_full[st]);
+          tc::mbar_arrive_expect_tx(full, kTile);
+          for (int sub = 0; sub < kSub; ++sub)
+            tma_load_3d(tc::smem_u32(sV + st * kTile + sub * kSubBytes), &tm_v, full, hkv * D + sub * 64, vj * kRows, b);
+          ++vj;
         }
-        ++issued;
       }
       if (!ok) {
         // drain: wait (bounded) for the copies still in flight so that none lands after the block left
         const uint64_t t0 = tc::global_timer_ns();
         while (!tc::mbar_try_wait(tc::smem_u32(&bar_q), 0u) && tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
-        for (int i = max(0, issued - kStages); i < issued; ++i) {
-          const int st = i % kStages;
-          const uint32_t ph = (uint32_t)(i / kStages) & 1u;
-          while (!tc::mbar_try_wait(tc::smem_u32(&bar_kv_full[st]), ph) &&
+        for (int i = max(0, kj - kKS); i < kj; ++i)
+          while (!tc::mbar_try_wait(tc::smem_u32(&bar_k_full[i % kKS]), (uint32_t)(i / kKS) & 1u) &&
                  tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
-        }
+        for (int i = max(0, vj - kVS); i < vj; ++i)
+          while (!tc::mbar_try_wait(tc::smem_u32(&bar_v_full[i % kVS]), (uint32_t)(i / kVS) & 1u) &&
+                 tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
       }
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer ---------------------------------
-    if (lane == 0 && n_max > 0) {
-      bool ok = tc::mbar_wait(tc::smem_u32(&bar_q), 0u, abort);
+    // The whole warp runs the loop; only the tcgen05 instructions themselves are issued by one elected lane.
+    if (n_max > 0) {
+      bool ok = tc::mbar_wait_warp(tc::smem_u32(&bar_q), 0u, abort);
       // S_w = Q_w K^T: both operands K-major; D / 16 instructions of K = 16
       auto issue_s = [&](int w, int st) {
-        const uint32_t qa = tc::smem_u32(sQ + w * kTile), ka = tc::smem_u32(sKV + st * 2 * kTile);
+        const uint32_t qa = tc::smem_u32(sQ + w * kTile), ka = tc::smem_u32(sK + st * kTile);
+        const uint32_t d_tmem = tmem_base + kColS + (uint32_t)(w * 128);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (uint32_t)((ks / 4) * kSubBytes + (ks % 4) * 32);
-          tc::mma_ss<tc::MMA_F16>(tmem_base + kColS + (uint32_t)(w * 128), tc::smem_desc_k_major_sw128(qa + off),
-                                  tc::smem_desc_k_major_sw128(ka + off), prm.idesc_s, ks > 0 ? 1u : 0u);
+          const uint64_t da = tc::smem_desc_k_major_sw128(qa + off), db = tc::smem_desc_k_major_sw128(ka + off);
+          if (tc::elect_one()) tc::mma_ss<tc::MMA_F16>(d_tmem, da, db, prm.idesc_s, ks > 0 ? 1u : 0u);
         }
-        tc::mma_commit(tc::smem_u32(&bar_s_full[w]));
+        if (tc::elect_one()) tc::mma_commit(tc::smem_u32(&bar_s_full[w]));
       };
       // O_w = P_w V: P from tensor memory (8 packed columns per 16 keys), V MN-major (16 key rows per step)
       auto issue_pv = [&](int w, int st, int j) {
-        const uint32_t va = tc::smem_u32(sKV + st * 2 * kTile + kTile);
+        const uint32_t va = tc::smem_u32(sV + st * kTile);
+        const uint32_t d_tmem = tmem_base + kColO + (uint32_t)(w * 128), a_tmem = tmem_base + kColS + (uint32_t)(w * 128);
 #pragma unroll
-        for (int t = 0; t < kRows / 16; ++t)
-          mma_ts_f16(tmem_base + kColO + (uint32_t)(w * 128), tmem_base + kColS + (uint32_t)(w * 128 + t * 8),
-                     smem_desc_mn_major_sw128(va + (uint32_t)(t * 16 * 128), kSubBytes, 1024), prm.idesc_pv,
-                     (j > 0 || t > 0) ? 1u : 0u);
-        if (j == n_tiles[w] - 1) tc::mma_commit(tc::smem_u32(&bar_o_full[w]));        // the row's last tile: O complete
+        for (int t = 0; t < kRows / 16; ++t) {
+          const uint64_t db = smem_desc_mn_major_sw128(va + (uint32_t)(t * 16 * 128), kSubBytes, 1024);
+          if (tc::elect_one()) mma_ts_f16(d_tmem, a_tmem + (uint32_t)(t * 8), db, prm.idesc_pv, (j > 0 || t > 0) ? 1u : 0u);
+        }
+        if (j == n_tiles[w] - 1 && tc::elect_one()) tc::mma_commit(tc::smem_u32(&bar_o_full[w]));   // last tile: O complete
       };
-      if (ok) ok = tc::mbar_wait(tc::smem_u32(&bar_kv_full[0]), 0u, abort);
+      // the last query tile that reads key tile t (the second one sees at least as many tiles as the
+      // first, unless it lies beyond the sequence altogether)
+      auto last_user = [&](int t) { return t < n_tiles[1] ? 1 : 0; };
+      if (ok) ok = tc::mbar_wait_warp(tc::smem_u32(&bar_k_full[0]), 0u, abort);
       if (ok) {
         tc::fence_after_sync();
         for (int w = 0; w < 2; ++w)
           if (n_tiles[w] > 0) issue_s(w, 0);
+        if (tc::elect_one()) tc::mma_commit(tc::smem_u32(&bar_k_empty[0]));
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % kStages, st1 = (j + 1) % kStages;
-        const uint32_t ph1 = (uint32_t)((j + 1) / kStages) & 1u;
+        const int vs = j % kVS, ks1 = (j + 1) % kKS;
+        const uint32_t vph = (uint32_t)(j / kVS) & 1u, kph1 = (uint32_t)((j + 1) / kKS) & 1u;
         for (int w = 0; w < 2 && ok; ++w) {
           if (j >= n_tiles[w]) continue;
-          if (!tc::mbar_wait(tc::smem_u32(&bar_p_ready[w]), (uint32_t)j & 1u, abort)) { ok = false; break; }
+          if (!tc::mbar_wait_warp(tc::smem_u32(&bar_p_ready[w]), (uint32_t)j & 1u, abort)) { ok = false; break; }
+          if (!tc::mbar_wait_warp(tc::smem_u32(&bar_v_full[vs]), vph, abort)) { ok = false; break; }
           tc::fence_after_sync();
-          issue_pv(w, st, j);
+          issue_pv(w, vs, j);
+          if (w == last_user(j) && tc::elect_one()) tc::mma_commit(tc::smem_u32(&bar_v_empty[vs]));      // V_j free once these retire
           if (j + 1 < n_tiles[w]) {
-            if (!tc::mbar_wait(tc::smem_u32(&bar_kv_full[st1]), ph1, abort)) { ok = false; break; }
-            issue_s(w, st1);
+            if (!tc::mbar_wait_warp(tc::smem_u32(&bar_k_full[ks1]), kph1, abort)) { ok = false; break; }
+            issue_s(w, ks1);
+            if (w == last_user(j + 1) && tc::elect_one()) tc::mma_commit(tc::smem_u32(&bar_k_empty[ks1]));   // K_{j+1} likewise
           }
         }
-        if (ok) tc::mma_commit(tc::smem_u32(&bar_kv_empty[st]));       // K_j and V_j are free once these MMAs retire
       }
     }
   }
@@ -307,17 +333,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(t_s + (uint32_t)(c * 32), v[c]);
       tc::tmem_ld_wait();
 
-      float mx = -INFINITY;
+      // row maximum: eight independent chains (a single chain of 128 dependent maxima is pure latency)
+      float mxs[8];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int i = 0; i < 8; ++i) mxs[i] = -INFINITY;
+      if (capped || need_mask) {                        // soft cap and mask applied in place (diagonal / last tile)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[c][i]);
-          if (capped) x = prm.softcap * tanhf(x * prm.scale / prm.softcap) / prm.scale;
-          if (need_mask && c * 32 + i >= limit) x = -INFINITY;
-          v[c][i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(v[c][i]);
+            if (capped) x = prm.softcap * tanhf(x * prm.scale / prm.softcap) / prm.scale;
+            if (need_mask && c * 32 + i >= limit) x = -INFINITY;
+            v[c][i] = __float_as_uint(x);
+            mxs[i & 7] = fmaxf(mxs[i & 7], x);
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(v[c][i]));
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                             fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
       // Move the reference only when the maximum has outgrown it by more than 2^8 (always on the first
       // tile).  tcgen05.ld / st are warp-wide, so the decision is taken per warp; a lane of a moving warp
       // moves to its own exact maximum.
@@ -325,25 +363,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mx);
         const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-        const float corr = fast_exp2((m_ref - m_safe) * sl);            // m_ref = -inf: 0
+        const float corr = m_new == m_ref ? 1.f : fast_exp2((m_ref - m_safe) * sl);     // m_ref = -inf: 0
         m_ref = m_new;
         l_run *= corr;
         if (j > 0) {                                    // O holds the tiles before this one: scale its row
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t ov[32];
-            tc::tmem_ld_32x32(t_o + (uint32_t)(c * 32), ov);
+#pragma unroll 1
+          for (int c = 0; c < D / 16; ++c) {            // (a rare path: short, rolled, few registers)
+            uint32_t ov[16];
+            tmem_ld_32x16(t_o + (uint32_t)(c * 16), ov);
             tc::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-            tmem_st_32x32(t_o + (uint32_t)(c * 32), ov);
+            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+            tmem_st_32x16(t_o + (uint32_t)(c * 16), ov);
           }
         }
       }
       const float neg_ms = m_ref == -INFINITY ? 0.f : -m_ref * sl;
 
       // P = exp2(s * sl - m * sl), row sum, packed 16-bit pairs into the first half of S
-      float psum0 = 0.f, psum1 = 0.f;
+      float ps[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ps[i] = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
@@ -351,13 +391,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int i = 0; i < 32; i += 2) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(v[c][i]), sl, neg_ms));       // masked: exp2(-inf) = 0
           const float p1 = fast_exp2(fmaf(__uint_as_float(v[c][i + 1]), sl, neg_ms));
-          psum0 += p0;
-          psum1 += p1;
+          ps[i & 7] += p0;
+          ps[(i & 7) + 1] += p1;
           pk[i / 2] = pack2<BF16>(p0, p1);
         }
         tmem_st_32x16(t_s + (uint32_t)(c * 16), pk);
       }
-      l_run += psum0 + psum1;
+      const float psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
+      l_run += psum;
       tmem_st_wait();
       tc::fence_before_sync();
       tc::mbar_arrive(tc::smem_u32(&bar_p_ready[w]));
@@ -482,3 +523,4 @@ extern "C" int llmqrt_attn_prefill(const void* q, int64_t q_token_stride, const 
   if (d == 128) return bf ? launch_prefill<true, 128>(tq, tk, tv, prm, B, st) : launch_prefill<false, 128>(tq, tk, tv, prm, B, st);
   return bf ? launch_prefill<true, 64>(tq, tk, tv, prm, B, st) : launch_prefill<false, 64>(tq, tk, tv, prm, B, st);
 }
+

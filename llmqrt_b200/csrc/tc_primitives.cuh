@@ -88,6 +88,20 @@ __device__ __forceinline__ void mbar_wait_or_flag(uint32_t bar, uint32_t parity,
       : "memory");
 }
 
+// One lane of a fully converged warp.  The issuing warp runs its loop with all 32 lanes and guards only
+// the asynchronous instruction itself with this: the operands (descriptors, addresses) are then
+// computed in warp-uniform code, where the compiler can keep them in uniform registers -- computed
+// under `if (lane == 0)` they have to be moved there one by one for every instruction issued.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+// Bounded wait executed by every lane of a converged warp; the result is warp-uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort));
+}
+
 // Named barrier over `nthreads` threads that also ORs a predicate across them (uniform result).
 __device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool pred) {
   uint32_t r;
