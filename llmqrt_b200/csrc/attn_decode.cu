@@ -147,7 +147,8 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
                    const uint16_t* __restrict__ v_cache, int64_t cache_batch_stride, int64_t cache_row_stride,
                    const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int Hkv, int chunk,
                    int max_splits, int max_len, float scale, float softcap, float* __restrict__ part_o,
-                   float* __restrict__ part_ml, DecodeAppend ap) {
+                   float* __restrict__ part_ml, DecodeAppend ap, int8_t* __restrict__ out_q,
+                   float* __restrict__ out_scale) {
   constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
   constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
   LLMQRT_TIMELINE_MARK(40);
@@ -379,6 +380,12 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
     }
   __syncthreads();
 
+  // out_q (only passed when this block holds the sequence's WHOLE token row: one KV head, no splits):
+  // the per-token int8 quantization of the row is done right here and the merge kernel is not launched.
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  __shared__ uint16_t row_bits[8 * D];
+  __shared__ float red_amax[kWarps];
+  float amax = 0.f;
   for (int i = tid; i < rep * D; i += kThreads) {
     const int hd = i / D, dd = i - hd * D;
     float M = -INFINITY;
@@ -400,6 +407,10 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
       if constexpr (BF16) { __nv_bfloat16 hv = __float2bfloat16_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
       else { __half hv = __float2half_rn(r); bits = *reinterpret_cast<uint16_t*>(&hv); }
       out[((int64_t)b * Hq + hq) * D + dd] = bits;
+      if (out_q) {
+        row_bits[i] = bits;
+        amax = fmaxf(amax, fabsf(bits_to_f32<BF16>(bits)));
+      }
     } else {
       const int64_t slot = ((int64_t)b * Hq + hq) * max_splits + split;
       part_o[slot * D + dd] = osum;
@@ -407,6 +418,22 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
         part_ml[slot * 2] = M;
         part_ml[slot * 2 + 1] = lsum;
       }
+    }
+  }
+  if (out_q) {                                       // block-uniform; the arithmetic of the stand-alone per-token quantizer
+    amax = warp_max(amax);
+    if (lane == 0) red_amax[warp] = amax;
+    __syncthreads();
+    amax = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) amax = fmaxf(amax, red_amax[w]);
+    float sc = round_to<T>(fmaxf(amax, 1e-5f));
+    sc = round_to<T>(__fmul_rn(sc, 1.0f / 127.0f));
+    if (tid == 0) out_scale[b] = sc;
+    for (int i = tid; i < rep * D; i += kThreads) {
+      float v = rintf(round_to<T>(__fdiv_rn(bits_to_f32<BF16>(row_bits[i]), sc)));
+      v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
+      out_q[(int64_t)b * Hq * D + i] = (int8_t)(int)v;         // Hkv == 1: the block's rows are the whole token row
     }
   }
 }
@@ -486,11 +513,15 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   static_assert(smem >= kWarps * 8 * D * 4, "ring too small for the merge tile");
   auto kern = attn_decode_kernel<BF16, D>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
-  const bool need_merge = max_splits > 1 || out_q != nullptr;
+  // One KV head and no splits (a tensor-parallel rank that holds a single KV head): the attention block
+  // of a sequence produces the whole token row and quantizes it itself -- one kernel less per layer.
+  const bool quant_in_kernel = out_q != nullptr && Hkv == 1 && max_splits == 1 && Hq <= 8;
+  const bool need_merge = max_splits > 1 || (out_q != nullptr && !quant_in_kernel);
   if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
                               reinterpret_cast<const uint16_t*>(q), qbs, reinterpret_cast<const uint16_t*>(kc),
                               reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
-                              Hq, Hkv, chunk, max_splits, max_seqlen, scale, softcap, part_o, part_ml, ap))
+                              Hq, Hkv, chunk, max_splits, max_seqlen, scale, softcap, part_o, part_ml, ap,
+                              quant_in_kernel ? out_q : (int8_t*)nullptr, quant_in_kernel ? out_scale : (float*)nullptr))
     return rc;
   if (int rc = check_launch("attn_decode")) return rc;
   if (need_merge) {

@@ -12,10 +12,12 @@
 // Dequantization is then  (h + (-(1024+zero))) * scale  = exactly fp16((v - zero) * scale): the
 // subtraction is exact and the product is rounded once, like the reference's kernels.
 //
-// The GEMM is computed transposed (weights are the 16-row MMA operand, tokens the 8-column one),
-// each warp owns 32 weight rows so that one activation fragment feeds two weight fragments, and the
-// reduction dimension is split across blocks with a deterministic last-arriver fix-up.
-#include "common.cuh"
+// The decode-sized GEMM (M <= 64) is computed transposed (weights are the 16-row MMA operand, tokens the
+// 8-column one), each warp owns 32 weight rows so that one activation fragment feeds two weight
+// fragments, and the reduction dimension is split across blocks with a deterministic last-arriver
+// fix-up.  Above 64 tokens the same entry point runs the TMA + tcgen05 GEMM kernel with the weight
+// operand dequantized tile by tile into shared memory by extra warps of that kernel (gemm_tc.cu).
+#include "gemm_w8a8.cuh"
 
 namespace llmqrt {
 namespace {
@@ -355,6 +357,14 @@ int llmqrt_awq_gemm(const void* x, int64_t ldx, const uint32_t* wq_t, const uint
   e.ldo = ldo;
   const __half* xp = reinterpret_cast<const __half*>(x);
   cudaStream_t st = (cudaStream_t)stream;
+  if (M > 64) {
+    // Prefill-sized M: still ONE kernel.  The tcgen05 GEMM runs with four extra warps that turn the
+    // packed 4-bit tiles into fp16 operand tiles in shared memory (same rounding: fp16((v - z) * s)),
+    // so the dequantized weights never exist in global memory.
+    e.out = out;
+    const AwqOperand op = {wq_t, sz_t, group_size};
+    return gemm_tc(KIND_F16, x, ldx, nullptr, 0, M, N, K, e, workspace, st, false, &op);
+  }
   for (int64_t m0 = 0; m0 < M; m0 += 32) {       // token panels of 32: larger M re-streams the weights per panel
     const int mc = (int)((M - m0 < 32) ? (M - m0) : 32);
     e.out = reinterpret_cast<__half*>(out) + m0 * ldo;

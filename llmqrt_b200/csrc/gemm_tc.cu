@@ -42,6 +42,7 @@ namespace llmqrt {
 namespace {
 
 constexpr int kThreads = 192;
+constexpr int kThreadsAwq = kThreads + 128;   // + four warps that dequantize the 4-bit weight tiles
 constexpr int kBM = 128;           // rows of P per tile (UMMA M)
 constexpr int kRowBytes = 128;     // bytes of K per stage row (one swizzle span)
 constexpr int kSmemBudget = 226 * 1024;   // of the 227 KiB a block may use
@@ -58,6 +59,12 @@ struct TcParams {
   uint32_t idesc;
   unsigned* status;                // set to 1 if a bounded wait ran out
   Epilogue epi;
+  // AWQ mode: the weight operand is not fetched by TMA but produced in shared memory by four extra
+  // warps from the packed 4-bit layer (wq_t [N, K/8] words of eight K-consecutive values, sz_t
+  // [N, K/G] half2 {scale, -(1024 + zero)}, see awq.cu)
+  const uint32_t* awq_w;
+  const uint32_t* awq_sz;
+  int awq_kw, awq_kg, awq_g;       // K / 8, K / G, G
 };
 
 template <int BN> constexpr int stage_bytes() { return (kBM + BN) * kRowBytes; }
@@ -310,9 +317,10 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
 __device__ unsigned long long g_last_done;   // latest exit time over the blocks of the launch in flight
 #endif
 
-template <int KIND, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int KIND, int BN, bool AWQ = false>
+__global__ void __launch_bounds__(AWQ ? kThreadsAwq : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q, TcParams prm) {
+  static_assert(!AWQ || KIND == tc::MMA_F16, "the 4-bit weights dequantize to fp16");
   using AccT = typename std::conditional<KIND == tc::MMA_I8, int, float>::type;
   constexpr int kStages = num_stages<BN>();
   constexpr int kStageBytes = stage_bytes<BN>();
@@ -356,7 +364,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     abort_flag = 0;
     cluster_abort = 0;
     for (int s = 0; s < kStages; ++s) {
-      tc::mbar_init(tc::smem_u32(&bar_full[s]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_full[s]), AWQ ? 5 : 1);           // AWQ: + one arrival per dequantizing warp
       tc::mbar_init(tc::smem_u32(&bar_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -414,6 +422,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       // preceding kernel has just produced (a weight quantized on the fly, an AWQ layer dequantized
       // for a large M) must be waited for like the activations.
       const bool early_w = prm.early_w != 0;
+      // AWQ: only the activation tile arrives by TMA (the weight tile is written by the dequantizing warps)
+      const bool tma_p = !(AWQ && prm.swap != 0), tma_q = !(AWQ && prm.swap == 0);
+      const uint32_t tx_bytes = AWQ ? (uint32_t)((prm.swap ? BN : kBM) * kRowBytes) : (uint32_t)kStageBytes;
       if (!early_w) {
         pdl_wait();
         TC_TRACE(12);
@@ -430,9 +441,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           const int x = (kb_begin + kr) * kXPerBlock;
           const uint32_t full = tc::smem_u32(&bar_full[g]);
           uint8_t* sp = tiles + g * kStageBytes;
-          if (phase_w) tc::mbar_arrive_expect_tx(full, kStageBytes);
-          if (load_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
-          else tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
+          if (phase_w) tc::mbar_arrive_expect_tx(full, tx_bytes);
+          if (load_p) { if (tma_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM); }
+          else if (tma_q) tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
         }
         if (phase_w && early_w) {
           // (Prefetching further weight tiles into L2 here was measured to slow the kernel down: the
@@ -468,10 +479,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
             const int kb = kb_begin + kr;
             const uint32_t full = tc::smem_u32(&bar_full[stage_i]);
             uint8_t* sp = tiles + stage_i * kStageBytes;
-            tc::mbar_arrive_expect_tx(full, kStageBytes);
+            tc::mbar_arrive_expect_tx(full, tx_bytes);
             const int x = kb * kXPerBlock;
-            tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
-            tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
+            if (tma_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
+            if (tma_q) tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
             ++issued;
             if (++stage_i == kStages) { stage_i = 0; phase ^= 1u; }
           }
@@ -524,6 +535,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         TC_TRACE(3);
         acc_phase[buf] ^= 1u;
         buf ^= 1;
+      }
+    }
+  } else if (AWQ && warp >= 6) {
+    // ------------------------------- AWQ weight producer -------------------------
+    // Thread t fills rows t (and t + 128 of a 256-row tile) of the weight tile of every stage: eight
+    // packed words (64 values of K) -> eight 16-byte chunks of fp16, stored at the 128-byte-swizzle
+    // positions a TMA load would have used, then made visible to the tensor core (async proxy) before
+    // the warp's arrival.  The packed words of the next kDepth K blocks are already in registers when a
+    // block is dequantized (a load from L2 takes longer than the tensor core needs for a block).
+    constexpr int kRpt = BN > kBM ? BN / kBM : 1;      // rows per thread (two for 256-row weight tiles)
+    constexpr int kDepth = 4;
+    const int t = (int)threadIdx.x - 6 * 32;
+    const int rpt = prm.swap ? 1 : kRpt;
+    const int w_off = prm.swap ? 0 : kBM * kRowBytes;  // offset of the weight tile inside a stage
+    const int n_limit = prm.N;
+    const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
+    const int total = my_tiles * kb_count;             // K blocks this CTA consumes, in ring order
+    uint32_t words[kDepth][kRpt][8];
+    uint32_t szv[kDepth][kRpt][2];                     // {scale, -(1024 + zero)} of words 0-3 and of words 4-7
+    auto fetch = [&](int q, uint32_t (&w)[kRpt][8], uint32_t (&z)[kRpt][2]) {
+      const int tile = first_tile + (q / kb_count) * tile_step, it = q % kb_count;
+      const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
+      int kr = it + (tp * 5 + tq * 3) % kb_count;      // the producer's K rotation
+      if (kr >= kb_count) kr -= kb_count;
+      const int kb = kb_begin + kr;                    // words 8 kb .. 8 kb + 7 of a row
+      const int n0 = prm.swap ? tp * kBM : tq * BN;
+#pragma unroll
+      for (int r = 0; r < kRpt; ++r) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[r][j] = 0u;
+        z[r][0] = z[r][1] = 0u;
+        const int n = n0 + t + r * kBM;
+        if (r < rpt && q < total && n < n_limit) {
+          const uint32_t* src = prm.awq_w + (int64_t)n * prm.awq_kw + kb * 8;
+          if (kb * 8 + 8 <= prm.awq_kw) {
+            const uint4 a = ldg_stream_16B(src), c = ldg_stream_16B(src + 4);
+            w[r][0] = a.x; w[r][1] = a.y; w[r][2] = a.z; w[r][3] = a.w;
+            w[r][4] = c.x; w[r][5] = c.y; w[r][6] = c.z; w[r][7] = c.w;
+          } else {                                     // K ends inside this block: the rest stays zero
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (kb * 8 + j < prm.awq_kw) w[r][j] = src[j];
+          }
+          const uint32_t* zs = prm.awq_sz + (int64_t)n * prm.awq_kg;
+          z[r][0] = __ldg(zs + (kb * 64) / prm.awq_g);
+          if (kb * 8 + 4 < prm.awq_kw) z[r][1] = __ldg(zs + (kb * 64 + 32) / prm.awq_g);
+        }
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) fetch(d, words[d], szv[d]);
+    int stage_i = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int q0 = 0; q0 < total && ok; q0 += kDepth) {
+#pragma unroll
+      for (int d = 0; d < kDepth; ++d) {
+        if (q0 + d >= total || !ok) continue;
+        tc::mbar_wait_or_flag(tc::smem_u32(&bar_empty[stage_i]), phase ^ 1u, abort_u32);
+        if (*abort) { ok = false; continue; }
+        uint8_t* wt = tiles + stage_i * kStageBytes + w_off;
+#pragma unroll
+        for (int r = 0; r < kRpt; ++r) {
+          if (r >= rpt) continue;
+          const int rr = t + r * kBM;
+          uint4* dst = reinterpret_cast<uint4*>(wt + rr * kRowBytes);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            // words of a row beyond K or N were fetched as zero with scale 0: (1024 + 0 - 0) * 0 = 0
+            const __half2 sz = *reinterpret_cast<const __half2*>(&szv[d][r][j >> 2]);
+            const __half2 negz = __half2half2(__high2half(sz)), sc = __half2half2(__low2half(sz));
+            uint32_t o[4];
+#pragma unroll
+            for (int p4 = 0; p4 < 4; ++p4) {
+              uint32_t h = ((words[d][r][j] >> (4 * p4)) & 0x000F000Fu) | 0x64006400u;   // {1024 + v[2p], 1024 + v[2p+1]}
+              const __half2 v2 = __hmul2(__hadd2(*reinterpret_cast<__half2*>(&h), negz), sc);
+              o[p4] = *reinterpret_cast<const uint32_t*>(&v2);
+            }
+            dst[j ^ (rr & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(tc::smem_u32(&bar_full[stage_i]));
+        if (++stage_i == kStages) { stage_i = 0; phase ^= 1u; }
+        fetch(q0 + d + kDepth, words[d], szv[d]);      // refill the slot for kDepth blocks ahead
       }
     }
   } else {
@@ -590,9 +687,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     uint32_t* send = reinterpret_cast<uint32_t*>(tiles + BN * kBM * 4);
     const bool own_healthy = abort_flag == 0;          // own MMAs finished (epilogue warps waited for them)
     const int quad = warp & 3, et = quad * 32 + lane;
+    const bool epi_warp = warp >= 2 && warp < 6;       // (AWQ mode has four more warps behind them)
     const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
     const EpiConsts& ec = ec_split;                    // q_scale / q_bias cover only the columns this CTA owns
-    if (warp >= 2 && own_healthy) {
+    if (epi_warp && own_healthy) {
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
       // 32 columns per round trip to tensor memory (four loads in flight before the wait): the
       // wait, not the data volume, is what each round costs
@@ -642,12 +740,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       for (int o = 0; o < S; ++o) mbar_arrive_remote(tc::smem_u32(&bar_release), (uint32_t)o);
     }
     bool reduce_ok = false;
-    if (warp >= 2) {
+    if (epi_warp) {
       const bool failed = !healthy || !tc::mbar_wait(tc::smem_u32(&bar_reduce), 0u, abort);
       reduce_ok = !tc::named_barrier_or(2, 128, failed);
     }
     if (threadIdx.x == 64) TC_TRACE(9);
-    if (warp >= 2 && reduce_ok) {
+    if (epi_warp && reduce_ok) {
       const AccT* rbuf = reinterpret_cast<const AccT*>(tiles);
 #pragma unroll 1
       for (int c0 = 0; c0 < cpo; c0 += kChunk) {
@@ -741,11 +839,11 @@ int make_operand_map(CUtensorMap* map, const void* base, int elt_bytes, int64_t 
   return LLMQRT_OK;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool AWQ = false>
 cudaLaunchConfig_t make_config(int grid, int cluster, cudaStream_t st, cudaLaunchAttribute* attr) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(AWQ ? kThreadsAwq : kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes<BN>();
   cfg.stream = st;
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -763,7 +861,7 @@ cudaLaunchConfig_t make_config(int grid, int cluster, cudaStream_t st, cudaLaunc
 }
 
 // How many clusters of `cluster` CTAs of this kernel can be resident at once (cached per device).
-template <int KIND, int BN>
+template <int KIND, int BN, bool AWQ = false>
 int max_active_clusters(int cluster) {
   static std::mutex mu;
   static std::map<std::pair<int, int>, int> cache;
@@ -772,11 +870,11 @@ int max_active_clusters(int cluster) {
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find({dev, cluster});
   if (it != cache.end()) return it->second;
-  auto kern = gemm_tc_kernel<KIND, BN>;
+  auto kern = gemm_tc_kernel<KIND, BN, AWQ>;
   int n = 0;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>()) == LLMQRT_OK) {
     cudaLaunchAttribute attr[2];
-    cudaLaunchConfig_t cfg = make_config<KIND, BN>(cluster, cluster, nullptr, attr);
+    cudaLaunchConfig_t cfg = make_config<KIND, BN, AWQ>(cluster, cluster, nullptr, attr);
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
       cudaGetLastError();
       n = 0;
@@ -786,9 +884,9 @@ int max_active_clusters(int cluster) {
   return n;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool AWQ = false>
 int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaStream_t st) {
-  auto kern = gemm_tc_kernel<KIND, BN>;
+  auto kern = gemm_tc_kernel<KIND, BN, AWQ>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>())) return rc;
   const int sms = sm_count();
   const int tiles = prm.tiles_p * prm.tiles_q;
@@ -801,7 +899,7 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaS
     float best = (float)ceil_div(tiles, sms) * ((float)prm.k_blocks + fixed);
     for (int s = 2; s <= 8; s *= 2) {
       if (prm.k_blocks < 2 * s || BN % s != 0 || BN / s < 8) continue;
-      const int active = max_active_clusters<KIND, BN>(s);
+      const int active = max_active_clusters<KIND, BN, AWQ>(s);
       if (active <= 0) continue;
       const float t = (float)ceil_div(tiles, active) * ((float)prm.k_blocks / s + fixed);
       if (t < best) { best = t; splits = s; }
@@ -810,26 +908,33 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaS
   prm.splits = splits;
   const int grid = splits > 1 ? tiles * splits : (tiles < sms ? tiles : sms);
   cudaLaunchAttribute attr[2];
-  cudaLaunchConfig_t cfg = make_config<KIND, BN>(grid, splits, st, attr);
+  cudaLaunchConfig_t cfg = make_config<KIND, BN, AWQ>(grid, splits, st, attr);
   LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_p, tm_q, prm));
   return check_launch("gemm_tc");
 }
 
-template <int KIND>
+template <int KIND, bool AWQ = false>
 int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const TcParams& prm, cudaStream_t st) {
   switch (bn) {
-    case 32: return launch<KIND, 32>(tm_p, tm_q, prm, st);
-    case 64: return launch<KIND, 64>(tm_p, tm_q, prm, st);
-    case 128: return launch<KIND, 128>(tm_p, tm_q, prm, st);
-    default: return launch<KIND, 256>(tm_p, tm_q, prm, st);
+    case 32: return launch<KIND, 32, AWQ>(tm_p, tm_q, prm, st);
+    case 64: return launch<KIND, 64, AWQ>(tm_p, tm_q, prm, st);
+    case 128: return launch<KIND, 128, AWQ>(tm_p, tm_q, prm, st);
+    default: return launch<KIND, 256, AWQ>(tm_p, tm_q, prm, st);
   }
 }
 
 }  // namespace
 
 int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
-            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w) {
+            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w, const AwqOperand* awq) {
   const int elt = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
+  if (awq) {                                           // W is produced in shared memory from the packed layer
+    LLMQRT_REQUIRE(kind == KIND_F16 && awq->wq_t && awq->sz_t && awq->G > 0 && K % 8 == 0 && K % awq->G == 0 &&
+                   awq->G % 8 == 0, "tcgen05 awq gemm: fp16 activations, K and group size multiples of 8");
+    W = A;                                             // placeholder for the unused tensor map
+    ldw = lda;
+    static_w = false;
+  }
   LLMQRT_REQUIRE((K * elt) % 16 == 0 && (lda * elt) % 16 == 0 && (ldw * elt) % 16 == 0,
                  "tcgen05 gemm: K and leading dimensions must cover multiples of 16 bytes");
   LLMQRT_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0,
@@ -878,6 +983,14 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   if (int rc = make_operand_map(&tm_p, p_base, elt, prm.rows_p, K, prm.swap ? ldw : lda, kBM)) return rc;
   if (int rc = make_operand_map(&tm_q, q_base, elt, prm.rows_q, K, prm.swap ? lda : ldw, bn)) return rc;
 
+  if (awq) {
+    prm.awq_w = awq->wq_t;
+    prm.awq_sz = awq->sz_t;
+    prm.awq_kw = (int)(K / 8);
+    prm.awq_kg = (int)(K / awq->G);
+    prm.awq_g = (int)awq->G;
+    return launch_bn<tc::MMA_F16, true>(bn, tm_p, tm_q, prm, st);
+  }
   if (mk == tc::MMA_I8) return launch_bn<tc::MMA_I8>(bn, tm_p, tm_q, prm, st);
   if (mk == tc::MMA_F8) return launch_bn<tc::MMA_F8>(bn, tm_p, tm_q, prm, st);
   return launch_bn<tc::MMA_F16>(bn, tm_p, tm_q, prm, st);

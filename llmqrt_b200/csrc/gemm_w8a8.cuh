@@ -19,8 +19,16 @@ int w8a8_gemm_stream(int kind, const uint8_t* A, int64_t lda, const uint8_t* W, 
 // TMA + tcgen05/TMEM kernel (gemm_tc.cu): any M; lda/ldw in elements.  static_w: W is a stored weight
 // that nothing queued on the stream writes, so its first tiles may be requested before the
 // preceding kernel of the stream has completed.
+// awq != nullptr (kind KIND_F16): W / ldw are ignored and the weight operand is dequantized on the fly,
+// tile by tile, from the repacked 4-bit layer (layouts: awq.cu) by extra warps of the same kernel.
+struct AwqOperand {
+  const uint32_t* wq_t;   // [N, K/8]
+  const uint32_t* sz_t;   // [N, K/G]
+  int64_t G;
+};
 int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
-            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w = false);
+            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w = false,
+            const AwqOperand* awq = nullptr);
 
 // Path selection shared by all entry points (0 auto, 1 streaming, 2 tcgen05).
 int gemm_path();

@@ -168,11 +168,6 @@ def gemm_16bit(a, w, bias=None) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 # AWQ W4A16
 # ---------------------------------------------------------------------------------------------
-# Above this many tokens the weights are dequantized once and multiplied by the tcgen05 fp16 GEMM;
-# at or below it the streaming dequant-GEMM reads the 4-bit weights directly.
-AWQ_STREAM_MAX_M = 64
-
-
 def awq_dequantize(qweight, scales, qzeros) -> torch.Tensor:
     """W[K, N] in scales.dtype from the reference storage layout."""
     dev = L.require_cuda(qweight, scales, qzeros)
@@ -214,14 +209,13 @@ def awq_dequantize_t(packed: AwqPacked) -> torch.Tensor:
 
 
 def awq_gemm(x: torch.Tensor, packed: AwqPacked, bias=None) -> torch.Tensor:
-    """C[M, N] fp16 = x[M, K] fp16 @ dequant(W) (+ bias)."""
+    """C[M, N] fp16 = x[M, K] fp16 @ dequant(W) (+ bias): one fused kernel at every M (a weight-streaming
+    mma.sync kernel up to 64 tokens, the tcgen05 GEMM with in-kernel dequantization above)."""
     dev = L.require_cuda(x, packed.wq_t, bias)
     x2 = _rows(x)
     M, K = x2.shape
     if K != packed.K:
         raise RuntimeError(f"awq_gemm: x has K={K}, layer has K={packed.K}")
-    if M > AWQ_STREAM_MAX_M:
-        return gemm_16bit(x2, awq_dequantize_t(packed), bias)
     out = torch.empty((M, packed.N), dtype=torch.float16, device=dev)
     with torch.cuda.device(dev):
         L.call("llmqrt_awq_gemm", L.ptr(x2), x2.stride(0), L.ptr(packed.wq_t), L.ptr(packed.sz_t), L.ptr(bias),

@@ -43,19 +43,146 @@ def rows_of_heads(heads: list[int], head_dim: int) -> list[int]:
     return [h * head_dim + i for h in heads for i in range(head_dim)]
 
 
+# ---------------------------------------------------------------------------------------------
+# Sharding of a loaded state dict (buffer names and layouts of the reference's linear classes:
+# runtime/nn_models/modules/linear/linear_awq.py:97-131, linear_sq.py:77-88, linear_fp8.py:152-164;
+# the loader that fills them: runtime/core/base.py:306-340)
+# ---------------------------------------------------------------------------------------------
+def split_points(total: int, parts: int, unit: int = 1) -> list[int]:
+    """Boundaries 0 = b[0] <= ... <= b[parts] = total, every one a multiple of `unit`, as even as the
+    unit allows (the leading parts get the extra units).  E.g. the 18944 input channels of Qwen2-7B's
+    down_proj in AWQ groups of 128 on 8 ranks: 148 groups -> 19,19,19,19,18,18,18,18 groups."""
+    if total % unit:
+        raise ValueError(f"{total} is not a multiple of the unit {unit}")
+    units = total // unit
+    base, extra = divmod(units, parts)
+    out = [0]
+    for i in range(parts):
+        out.append(out[-1] + (base + (1 if i < extra else 0)) * unit)
+    return out
+
+
+def _as_index(sel, size: int) -> torch.Tensor:
+    if isinstance(sel, tuple):
+        return torch.arange(sel[0], sel[1])
+    idx = torch.as_tensor(sel, dtype=torch.int64).reshape(-1)
+    if idx.numel() and (int(idx.min()) < 0 or int(idx.max()) >= size):
+        raise ValueError("shard selection out of range")
+    return idx
+
+
+def _whole_blocks(idx: torch.Tensor, block: int, what: str) -> torch.Tensor:
+    """`idx` must consist of whole aligned runs of `block` consecutive values; returns the run numbers."""
+    if idx.numel() % block:
+        raise ValueError(f"{what}: selection must cover whole blocks of {block}")
+    runs = idx.reshape(-1, block)
+    if not (torch.equal(runs[:, 0] % block, torch.zeros_like(runs[:, 0])) and
+            torch.equal(runs, runs[:, :1] + torch.arange(block))):
+        raise ValueError(f"{what}: selection must cover whole aligned blocks of {block}")
+    return runs[:, 0] // block
+
+
+def shard_linear_state(state: dict, method: str, mode: str, sel, keep_bias: bool = True) -> dict:
+    """The shard of one quantized linear layer's state dict for Megatron tensor parallelism.
+
+    method: "awq" | "sq" | "fp8_static_quant" | "fp8_dynamic_quant" (the registry keys of
+            linear.method_to_linear).
+    mode:   "column" -- `sel` selects OUTPUT channels (q/k/v by heads, gate, up): weight rows, per-channel
+            scales and bias follow;  "row" -- `sel` selects INPUT channels (o_proj, down_proj): the
+            partial outputs of the ranks are summed afterwards, per-channel scales are replicated and
+            the bias is kept on one rank only (keep_bias).
+    sel:    (start, stop) or a 1-D index list / tensor (e.g. tp.rows_of_heads(...) for head-wise splits).
+    AWQ constraints: output channels travel in packed words of 8 columns, input channels in
+    quantization groups, so selections must cover whole aligned blocks of 8 (column) or of the group
+    size (row); split_points(..., unit=group_size) yields such row boundaries.
+    Per-tensor scalars (SmoothQuant per-tensor weight / input scales, FP8 per-tensor scales) are copied.
+    """
+    out = {}
+    if mode not in ("column", "row"):
+        raise ValueError("mode must be 'column' or 'row'")
+    if method == "awq":
+        qweight, qzeros, scales = state["qweight"], state["qzeros"], state["scales"]
+        K, N = qweight.shape[0], scales.shape[1]
+        G = K // scales.shape[0]
+        if mode == "column":
+            idx = _as_index(sel, N)
+            words = _whole_blocks(idx, 8, "awq column shard")
+            out["qweight"], out["qzeros"], out["scales"] = qweight[:, words], qzeros[:, words], scales[:, idx]
+        else:
+            idx = _as_index(sel, K)
+            groups = _whole_blocks(idx, G, "awq row shard")
+            out["qweight"], out["qzeros"], out["scales"] = qweight[idx], qzeros[groups], scales[groups]
+        n_axis = idx if mode == "column" else None
+    elif method in ("sq", "fp8_static_quant", "fp8_dynamic_quant"):
+        wname = "qweight" if method == "sq" else "weight"
+        w = state[wname]
+        N, K = w.shape
+        idx = _as_index(sel, N if mode == "column" else K)
+        out[wname] = w[idx] if mode == "column" else w[:, idx]
+        ws = state["weight_scale"]
+        out["weight_scale"] = (ws.reshape(N, -1)[idx].reshape((-1,) + tuple(ws.shape[1:]))
+                               if (mode == "column" and ws.numel() == N and N > 1) else ws)
+        for name in ("input_scale", "output_scale"):
+            if name in state:
+                out[name] = state[name]
+        n_axis = idx if mode == "column" else None
+    else:
+        raise ValueError(f"unknown quantization method {method!r}")
+    bias = state.get("bias")
+    if bias is not None:
+        if n_axis is not None:
+            out["bias"] = bias[n_axis]
+        else:
+            out["bias"] = bias if keep_bias else torch.zeros_like(bias)
+    return {k: (v.contiguous() if isinstance(v, torch.Tensor) else v) for k, v in out.items()}
+
+
+def shard_decoder_layer(layer_state: dict, method: str, num_heads: int, num_kv_heads: int, head_dim: int, tp: int,
+                        rank: int, prefix_map: dict | None = None) -> dict:
+    """Shards the seven linears of one Qwen2-style decoder layer: q/k/v by heads (head_assignment), gate/up by
+    output channels, o_proj / down_proj by the matching input channels.  `layer_state` maps the
+    projection names ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj") to
+    the state dicts of the layers; returns the same structure for this rank.  The intermediate
+    dimension is cut on multiples of the AWQ group size (or 16 for the 8-bit schemes)."""
+    names = prefix_map or {k: k for k in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")}
+    q_heads, kv_heads = head_assignment(num_heads, num_kv_heads, tp, rank)
+    q_idx, kv_idx = rows_of_heads(q_heads, head_dim), rows_of_heads(kv_heads, head_dim)
+    down = layer_state[names["down_proj"]]
+    if method == "awq":
+        inter = down["qweight"].shape[0]
+        unit = inter // down["scales"].shape[0]
+    else:
+        inter = down["qweight" if method == "sq" else "weight"].shape[1]
+        unit = 16
+    b = split_points(inter, tp, unit)
+    mlp = (b[rank], b[rank + 1])
+    out = {
+        names["q_proj"]: shard_linear_state(layer_state[names["q_proj"]], method, "column", q_idx),
+        names["k_proj"]: shard_linear_state(layer_state[names["k_proj"]], method, "column", kv_idx),
+        names["v_proj"]: shard_linear_state(layer_state[names["v_proj"]], method, "column", kv_idx),
+        names["o_proj"]: shard_linear_state(layer_state[names["o_proj"]], method, "row", q_idx, keep_bias=rank == 0),
+        names["gate_proj"]: shard_linear_state(layer_state[names["gate_proj"]], method, "column", mlp),
+        names["up_proj"]: shard_linear_state(layer_state[names["up_proj"]], method, "column", mlp),
+        names["down_proj"]: shard_linear_state(down, method, "row", mlp, keep_bias=rank == 0),
+    }
+    return out
+
+
 def greedy_select(val: torch.Tensor, idx: torch.Tensor, tp: int, group=None) -> torch.Tensor:
     """Vocabulary-parallel greedy sampling: every rank holds the best (value, global token id) of its
     vocabulary shard per row; returns the global argmax per row (ties go to the lowest rank, i.e. the
     lowest token id, like a single argmax over the full vocabulary)."""
     if tp == 1:
         return idx
-    vals = [torch.empty_like(val) for _ in range(tp)]
-    idxs = [torch.empty_like(idx) for _ in range(tp)]
-    torch.distributed.all_gather(vals, val.contiguous(), group=group)
-    torch.distributed.all_gather(idxs, idx.contiguous(), group=group)
-    vals, idxs = torch.stack(vals), torch.stack(idxs)
-    best = vals.float().argmax(dim=0, keepdim=True)
-    return idxs.gather(0, best)[0]
+    # one collective: (value, token id) pairs as fp32 (token ids below 2^24 are exact in fp32)
+    if int(idx.numel()) and val.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError("greedy_select: values must be floating point")
+    mine = torch.stack([val.float(), idx.float()], dim=-1).contiguous()            # [B, 2]
+    parts = [torch.empty_like(mine) for _ in range(tp)]
+    torch.distributed.all_gather(parts, mine, group=group)
+    both = torch.stack(parts)                                                      # [tp, B, 2]
+    best = both[..., 0].argmax(dim=0, keepdim=True)                                # first maximum = lowest rank
+    return both[..., 1].gather(0, best)[0].to(idx.dtype)
 
 
 class PeerAllreduce:

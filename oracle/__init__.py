@@ -19,8 +19,11 @@ Pinning status
 * The int8 / fp8 GEMM epilogues are pinned against the procedures of the
   reference's three unit tests (runtime/unittest/test_*.py): same shapes,
   same construction, same tolerances.
-* Attention: parity unpinned.  The reference delegates the arithmetic to the
-  un-vendored pip package flash-attn (only pin: the comment "2.4.2 -> 2.7.4"
-  at runtime/nn_models/modules/nonlinear/attn.py:11) and ships no test or
-  vector for it; the oracle restates the published operator semantics.
+* Attention: the reference delegates the arithmetic to the un-vendored pip
+  package flash-attn (only pin: the comment "2.4.2 -> 2.7.4" at
+  runtime/nn_models/modules/nonlinear/attn.py:11) and ships no test or
+  vector for it; the oracle restates the published operator semantics and is
+  pinned on the GPU against the installed flash_attn package called with the
+  reference's keyword sets (tests/test_gpu_attention_pin.py).  On a machine
+  without that package those tests skip and attention parity is unpinned.
 """

@@ -1,9 +1,10 @@
 """GQA attention over the KV cache, RoPE, RMSNorm (test oracle; see oracle/__init__.py).
 
-Attention parity is UNPINNED: the reference calls the third-party flash-attn
-package (runtime/nn_models/modules/nonlinear/attn.py:10-15, 290-315) and has
-no test or stored vector for it.  The functions below restate that package's
-documented operator semantics in fp32/fp64.
+The reference calls the third-party flash-attn package
+(runtime/nn_models/modules/nonlinear/attn.py:10-15, 290-315) and has no test
+or stored vector for it.  The functions below restate that package's
+documented operator semantics in fp32/fp64; tests/test_gpu_attention_pin.py
+pins them against the installed package on the GPU.
 """
 from __future__ import annotations
 

@@ -223,6 +223,27 @@ def test_decode_append_on_a_full_cache_writes_nothing():
         assert max_abs(out[:, 0], want) < ATTN_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Hq,lens,Smax", [(4, [1100, 1, 300, 0, 513], 1200), (3, [40, 7, 64], 64), (7, [200, 199], 256),
+                                           (4, [5000, 4097], 5100)])
+def test_decode_fused_quantization_single_kv_head(dtype, Hq, lens, Smax):
+    # one KV head (a tensor-parallel rank of 4 or 8): an unsplit sequence is quantized by the attention
+    # kernel itself, a split one by the merge kernel; both must be the per-token quantizer's bits
+    from llmqrt_b200.attention import attn_decode
+    from oracle import quant as oq
+    B, Hkv, d = len(lens), 1, 128
+    g = torch.Generator().manual_seed(Hq)
+    q = torch.randn(B, Hq, d, generator=g).to(dtype).cuda()
+    kc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()
+    vc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()
+    seqlens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    plain = attn_decode(q, kc, vc, seqlens, Smax)
+    out, out_q, scale = attn_decode(q, kc, vc, seqlens, Smax, quantize=True)
+    assert bits_equal(out, plain)
+    q_ref, s_ref = oq.quantize_int8(out.reshape(B, Hq * d).cpu(), per_token=True)
+    assert torch.equal(out_q.cpu(), q_ref) and torch.equal(scale.cpu(), s_ref.float().reshape(-1))
+
+
 def test_decode_quantization_single_split_without_workspace():
     # short caches need no split partials, hence no workspace; the merge kernel still quantizes the rows
     from llmqrt_b200 import _lib as L

@@ -59,7 +59,9 @@ def test_gemm_sweep(ops, M, N, K):
     assert rel_fro(y, ref.to(torch.float16)) < 1e-2
 
 
-@pytest.mark.parametrize("M", [3, 9, 17, 33, 64])
+# up to 64 tokens: the weight-streaming kernel; above: the tcgen05 kernel that dequantizes the weight
+# tiles in shared memory (K = 416 ends in half a 64-value block, N = 200 in a partial tile, groups of 32)
+@pytest.mark.parametrize("M", [3, 9, 17, 33, 64, 65, 100, 300, 1100])
 def test_gemm_ragged_shapes(ops, M):
     from oracle import awq as oa
     K, N, G = 416, 200, 32

@@ -94,3 +94,70 @@ def test_fused_attention_block_prefill_then_decode(double_append):
         ref1 = oa.attention_decode_kvcache(q1, kc, vc, None, None, lens)
     assert max_abs(w1.view(B, 1, H, d), ref1) < 2e-3
     assert torch.equal(attn.cache.k[:, :S + 1].cpu().view(torch.int16), kc[:, :S + 1].view(torch.int16))
+
+
+# ------------------------------------------------------------------ q/k/v and gate/up fusion
+def _quant_layers(method, shapes, K, seed):
+    """One quantized layer per (out_features, bias) in `shapes`, all reading K input channels."""
+    from llmqrt_b200.linear import FP8DynamicLinear, SqW8A8BBF16OBF16PerChannel, SqW8A8BBF16OBF16PerTensor, WQLinear_GEMM
+    layers = []
+    for i, (n, bias) in enumerate(shapes):
+        lin = _linear(K, n, bias, seed + i)
+        if method == "sq_channel":
+            layers.append(SqW8A8BBF16OBF16PerChannel.from_linear(lin, 8, 0, init_only=False, dtype=torch.bfloat16))
+        elif method == "sq_tensor":
+            layers.append(SqW8A8BBF16OBF16PerTensor.from_linear(lin, 8, 0, init_only=False, dtype=torch.float16))
+        elif method == "fp8_token":
+            layers.append(FP8DynamicLinear.from_linear(lin, 8, 0, init_only=False, dtype=torch.bfloat16, per_tensor=False))
+        elif method == "fp8_tensor":
+            layers.append(FP8DynamicLinear.from_linear(lin, 8, 0, init_only=False, dtype=torch.bfloat16, per_tensor=True))
+        else:
+            G = 128
+            wg = lin.weight.data.view(n, K // G, G)
+            scales = ((wg.amax(-1) - wg.amin(-1)).clamp_min(1e-5) / 15)
+            zeros = torch.round(-wg.amin(-1) / scales).clamp(0, 15)
+            layers.append(WQLinear_GEMM.from_linear(lin, 4, G, init_only=False, scales=scales.t().contiguous(),
+                                                    zeros=zeros.t().contiguous()))
+    return layers
+
+
+@pytest.mark.parametrize("method", ["sq_channel", "fp8_token", "awq"])
+@pytest.mark.parametrize("tokens", [7, 200])
+def test_fuse_qkv_equals_separate_projections(method, tokens):
+    # ref fused_utils.py:43-104 fuses AWQ only; the schemes with run-time activation scales fuse here too
+    from llmqrt_b200.fused_utils import fuse_qkv
+    from tests.util import bits_equal
+    K = 256
+    q, k, v = _quant_layers(method, [(512, True), (128, True), (128, True)], K, 20)
+    dt = torch.float16 if method == "awq" else torch.bfloat16
+    x = torch.randn(1, tokens, K, generator=torch.Generator().manual_seed(5)).to(dt).cuda()
+    want = torch.cat([q(x), k(x), v(x)], dim=-1)
+    fused = fuse_qkv(torch.nn.ModuleList([q, k, v]), q, k, v)
+    assert not isinstance(fused, tuple) and fused.out_features == 768
+    got = fused(x)
+    if method == "sq_channel":
+        assert bits_equal(got, want)              # exact integer accumulators, same fp32 epilogue per column
+    else:
+        assert rel_fro(got, want) < 2e-3          # fp32 sums may be split over K differently for another N
+
+
+@pytest.mark.parametrize("method", ["sq_tensor", "fp8_tensor"])
+def test_fuse_qkv_leaves_per_tensor_schemes_alone(method):
+    # q, k and v carry different per-tensor scales: like the reference (fused_utils.py:47-56) they stay separate
+    from llmqrt_b200.fused_utils import fuse_qkv
+    q, k, v = _quant_layers(method, [(256, True), (128, True), (128, True)], 256, 30)
+    out = fuse_qkv(torch.nn.ModuleList([q, k, v]), q, k, v)
+    assert isinstance(out, tuple) and out[0] is q and out[1] is k and out[2] is v
+
+
+@pytest.mark.parametrize("method", ["sq_channel", "awq"])
+def test_fused_gate_up_mlp(method):
+    from llmqrt_b200.fused_utils import FusedGateUpMLP
+    K, I = 256, 512
+    gate, up = _quant_layers(method, [(I, False), (I, False)], K, 40)
+    down = _quant_layers(method, [(K, False)], I, 50)[0]
+    dt = torch.float16 if method == "awq" else torch.bfloat16
+    x = torch.randn(3, 4, K, generator=torch.Generator().manual_seed(6)).to(dt).cuda()
+    want = down(torch.nn.functional.silu(gate(x)) * up(x))
+    got = FusedGateUpMLP(gate, up, down)(x)
+    assert got.shape == want.shape and rel_fro(got, want) < 1e-2

@@ -147,3 +147,108 @@ def test_oracle_tensor_parallel_emulation_matches_single_rank():
     l2 = Qwen2Oracle(Cfg, shards(2), 2, 8).forward(toks).float()
     assert l1.shape == l2.shape == (2, V)
     assert float((l1 - l2).norm() / l1.norm()) < 0.05
+
+
+# ---------------------------------------------------------------------------------------------
+# state-dict sharding (column / row tensor parallelism of loaded quantized layers)
+# ---------------------------------------------------------------------------------------------
+def test_split_points_respect_units():
+    from llmqrt_b200.tp import split_points
+    assert split_points(18944, 8, 128) == [0, 2432, 4864, 7296, 9728, 12032, 14336, 16640, 18944]   # 148 groups: 19 x 4 + 18 x 4
+    assert split_points(18944, 8, 16)[1] == 2368
+    assert split_points(96, 2, 16) == [0, 48, 96]
+    import pytest
+    with pytest.raises(ValueError):
+        split_points(100, 2, 16)
+
+
+def test_shard_linear_state_awq_blocks_and_errors():
+    import pytest
+    from llmqrt_b200.tp import shard_linear_state
+    from oracle import awq as oa
+    K, N, G = 256, 64, 64
+    qw, qz, sc = oa.random_layer(K, N, G, seed=3)
+    st = {"qweight": qw, "qzeros": qz, "scales": sc, "bias": torch.arange(N, dtype=torch.float16)}
+    w = oa.dequantize(qw, qz, sc, G)                                     # [K, N]
+    col = shard_linear_state(st, "awq", "column", (16, 48))
+    assert torch.equal(oa.dequantize(col["qweight"], col["qzeros"], col["scales"], G), w[:, 16:48])
+    assert torch.equal(col["bias"], st["bias"][16:48])
+    heads = list(range(8, 16)) + list(range(40, 48))                     # two separate aligned runs of 8 columns
+    col2 = shard_linear_state(st, "awq", "column", heads)
+    assert torch.equal(oa.dequantize(col2["qweight"], col2["qzeros"], col2["scales"], G), w[:, heads])
+    row = shard_linear_state(st, "awq", "row", (64, 192), keep_bias=False)
+    assert torch.equal(oa.dequantize(row["qweight"], row["qzeros"], row["scales"], G), w[64:192])
+    assert float(row["bias"].abs().max()) == 0
+    with pytest.raises(ValueError, match="whole"):
+        shard_linear_state(st, "awq", "column", (4, 36))                 # cuts through a packed word
+    with pytest.raises(ValueError, match="whole"):
+        shard_linear_state(st, "awq", "row", (32, 160))                  # cuts through a quantization group
+
+
+_SHARD_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from llmqrt_b200.tp import shard_decoder_layer, head_assignment
+from oracle import awq as oa, gemm as og, quant as oq
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[2], rank=int(sys.argv[3]), world_size=2)
+rank, tp = dist.get_rank(), 2
+H, Hq, Hkv, d, I, G = 128, 4, 2, 32, 256, 64
+g = torch.Generator().manual_seed(11)                                    # the same full checkpoint on every rank
+x = torch.randn(6, H, generator=g).to(torch.float16)
+
+def linear_sq(st, a):                                                    # per-token x per-channel int8 linear (CPU oracle)
+    aq, a_s = oq.quantize_int8(a, per_token=True)
+    return og.int8_linear_per_channel(aq, st["qweight"], st.get("bias"), a_s.float(), st["weight_scale"].float(), torch.float16)
+
+def linear_awq(st, a):
+    y = oa.gemm(a, st["qweight"], st["qzeros"], st["scales"], G)
+    return y if st.get("bias") is None else (y.float() + st["bias"].float()).to(torch.float16)
+
+def make_sq(n, k, bias):
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.float16)
+    q, s = oq.quantize_weight_int8_per_channel(w)
+    st = {"qweight": q, "weight_scale": s.float().reshape(-1)}
+    if bias: st["bias"] = (torch.randn(n, generator=g) * 0.1).to(torch.float16)
+    return st
+
+def make_awq(n, k, bias):
+    qw, qz, sc = oa.random_layer(k, n, G, seed=int(torch.randint(0, 1 << 30, (1,), generator=g)))
+    st = {"qweight": qw, "qzeros": qz, "scales": sc}
+    if bias: st["bias"] = (torch.randn(n, generator=g) * 0.1).to(torch.float16)
+    return st
+
+for method, make, lin, tol in (("sq", make_sq, linear_sq, 3e-2), ("awq", make_awq, linear_awq, 3e-3)):
+    full = {"q_proj": make(Hq * d, H, True), "k_proj": make(Hkv * d, H, True), "v_proj": make(Hkv * d, H, True),
+            "o_proj": make(H, Hq * d, False), "gate_proj": make(I, H, False), "up_proj": make(I, H, False),
+            "down_proj": make(H, I, True)}
+    mine = shard_decoder_layer(full, method, Hq, Hkv, d, tp, rank)
+    # column-parallel outputs are slices of the full outputs, bit for bit
+    qh, kh = head_assignment(Hq, Hkv, tp, rank)
+    q_full, q_mine = lin(full["q_proj"], x), lin(mine["q_proj"], x)
+    assert torch.equal(q_mine, q_full.view(6, Hq, d)[:, qh].reshape(6, -1)), method
+    # attention stand-in: this rank's q rows go through o_proj (row-parallel), then the MLP
+    o_part = lin(mine["o_proj"], q_mine).float()
+    dist.all_reduce(o_part)                                              # sum of the ranks' 16-bit partial outputs
+    o_full = lin(full["o_proj"], q_full).float()
+    err = float((o_part - o_full).norm() / o_full.norm())
+    assert err < tol, (method, "o_proj", err)
+    h = o_full.to(torch.float16)
+    act = lambda st: (torch.nn.functional.silu(lin(st["gate_proj"], h).float()) * lin(st["up_proj"], h).float()).to(torch.float16)
+    d_part = lin(mine["down_proj"], act(mine)).float()
+    dist.all_reduce(d_part)
+    d_full = lin(full["down_proj"], act(full)).float()
+    err = float((d_part - d_full).norm() / d_full.norm())
+    assert err < tol, (method, "down_proj", err)                         # (the bias is added once: kept on rank 0 only)
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_shard_decoder_layer_world_size_2_gloo(tmp_path):
+    script = tmp_path / "shard_worker.py"
+    script.write_text(_SHARD_WORKER)
+    port = str(29100 + os.getpid() % 300)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
