@@ -347,7 +347,7 @@ int llmqrt_awq_gemm(const void* x, int64_t ldx, const uint32_t* wq_t, const uint
                     llmqrt_stream_t stream) {
   if (int rc = check_layer(K, N, group_size)) return rc;
   LLMQRT_REQUIRE(x && wq_t && sz_t && out, "awq_gemm: null pointer");
-  LLMQRT_REQUIRE(K % 32 == 0 && group_size % 32 == 0, "awq_gemm: K and group size must be multiples of 32");
+  LLMQRT_REQUIRE(K % 32 == 0 && group_size % 32 == 0, "awq_gemm: K and group size must be multiples of 32");   // (a thread's 32 values of a K block share one group)
   LLMQRT_REQUIRE(ldx >= K && ldx % 8 == 0 && ldo >= N, "awq_gemm: bad leading dimension");
   LLMQRT_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(wq_t) & 15) == 0,
                  "awq_gemm: operands must be 16-byte aligned");

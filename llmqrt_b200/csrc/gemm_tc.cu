@@ -42,7 +42,8 @@ namespace llmqrt {
 namespace {
 
 constexpr int kThreads = 192;
-constexpr int kThreadsAwq = kThreads + 128;   // + four warps that dequantize the 4-bit weight tiles
+constexpr int kAwqWarps = 8;                  // warps that dequantize the 4-bit weight tiles (two per scheduler)
+constexpr int kThreadsAwq = kThreads + kAwqWarps * 32;
 constexpr int kBM = 128;           // rows of P per tile (UMMA M)
 constexpr int kRowBytes = 128;     // bytes of K per stage row (one swizzle span)
 constexpr int kSmemBudget = 226 * 1024;   // of the 227 KiB a block may use
@@ -77,6 +78,23 @@ template <int BN> constexpr int num_stages() {
   return s > 8 ? 8 : s;
 }
 template <int BN> constexpr int smem_bytes() { return num_stages<BN>() * stage_bytes<BN>() + kEpiStageBytes + 1024; }
+// AWQ mode (always with the weights as the 128-lane operand): every stage also holds the PACKED 4-bit
+// weight tile (32 bytes = 64 values of K per row, 128 rows) that TMA delivers and the dequantizing warps
+// expand into the stage's fp16 weight tile.  The output is 16-bit and transposed through a 32 x 128
+// staging tile, so the staging area is half the general one -- which buys the 256-token tile a fourth
+// pipeline stage.
+constexpr int kPackedRowBytes = 32;
+constexpr int kPackedBytes = kBM * kPackedRowBytes;
+constexpr int kEpiStageBytesAwq = 9 * 1024;            // kChunk rows x (128 x 2 B + 16 B pad)
+template <int BN> constexpr int num_stages_awq() {
+  constexpr int budget = BN > 128 ? kSmemBudget : 200 * 1024;
+  int s = (budget - 1024 - kEpiStageBytesAwq) / (stage_bytes<BN>() + kPackedBytes);
+  return s > 8 ? 8 : s;
+}
+template <int BN> constexpr int smem_bytes_awq() {
+  return num_stages_awq<BN>() * (stage_bytes<BN>() + kPackedBytes) + kEpiStageBytesAwq + 1024;
+}
+template <int BN, bool AWQ> constexpr int smem_bytes_of() { return AWQ ? smem_bytes_awq<BN>() : smem_bytes<BN>(); }
 template <int BN> constexpr uint32_t tmem_cols() { return 2 * BN < 32 ? 32 : 2 * BN; }
 
 template <typename AccT> __device__ __forceinline__ AccT acc_from_bits(uint32_t b);
@@ -319,11 +337,13 @@ __device__ unsigned long long g_last_done;   // latest exit time over the blocks
 
 template <int KIND, int BN, bool AWQ = false>
 __global__ void __launch_bounds__(AWQ ? kThreadsAwq : kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q, TcParams prm) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
+               const __grid_constant__ CUtensorMap tm_w, TcParams prm) {
   static_assert(!AWQ || KIND == tc::MMA_F16, "the 4-bit weights dequantize to fp16");
   using AccT = typename std::conditional<KIND == tc::MMA_I8, int, float>::type;
-  constexpr int kStages = num_stages<BN>();
+  constexpr int kStages = AWQ ? num_stages_awq<BN>() : num_stages<BN>();
   constexpr int kStageBytes = stage_bytes<BN>();
+  constexpr int kPkBytes = kPackedBytes;
   constexpr uint32_t kTmemCols = tmem_cols<BN>();
   constexpr int kBurst = kStages >= 8 ? 4 : (kStages >= 4 ? 2 : 1);  static_assert(BN > 128 || kStages * kStageBytes >= 2 * kBM * BN * 4, "ring too small for the reduce buffers");
   static_assert(kStages >= 3, "pipeline too shallow");
@@ -332,8 +352,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   // 1024-byte alignment is what the 128-byte swizzle pattern and the descriptors assume.
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage = tiles + kStages * kStageBytes;      // epilogue staging tile
+  uint8_t* packed = stage + (AWQ ? kEpiStageBytesAwq : kEpiStageBytes);   // AWQ: [kStages][kPkBytes] packed weight tiles
   __shared__ __align__(8) uint64_t bar_full[kStages];
   __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_pk[AWQ ? kStages : 1];   // AWQ: packed weight tile of the stage has landed
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ __align__(8) uint64_t bar_reduce;         // split mode: counts the bytes of the incoming slices
@@ -364,8 +386,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     abort_flag = 0;
     cluster_abort = 0;
     for (int s = 0; s < kStages; ++s) {
-      tc::mbar_init(tc::smem_u32(&bar_full[s]), AWQ ? 5 : 1);           // AWQ: + one arrival per dequantizing warp
+      tc::mbar_init(tc::smem_u32(&bar_full[s]), AWQ ? 1 + kAwqWarps : 1);   // AWQ: + one arrival per dequantizing warp
       tc::mbar_init(tc::smem_u32(&bar_empty[s]), 1);
+      if (AWQ) tc::mbar_init(tc::smem_u32(&bar_pk[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(tc::smem_u32(&bar_acc_full[b]), 1);
@@ -425,6 +448,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       // AWQ: only the activation tile arrives by TMA (the weight tile is written by the dequantizing warps)
       const bool tma_p = !(AWQ && prm.swap != 0), tma_q = !(AWQ && prm.swap == 0);
       const uint32_t tx_bytes = AWQ ? (uint32_t)((prm.swap ? BN : kBM) * kRowBytes) : (uint32_t)kStageBytes;
+      const uint32_t pk_bytes = (uint32_t)kPackedBytes;
       if (!early_w) {
         pdl_wait();
         TC_TRACE(12);
@@ -442,6 +466,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           const uint32_t full = tc::smem_u32(&bar_full[g]);
           uint8_t* sp = tiles + g * kStageBytes;
           if (phase_w) tc::mbar_arrive_expect_tx(full, tx_bytes);
+          if (AWQ && phase_w) {                        // packed 4-bit tile: words 8 kb .. 8 kb + 7 of the tile's weight rows
+            const uint32_t pk = tc::smem_u32(&bar_pk[g]);
+            tc::mbar_arrive_expect_tx(pk, pk_bytes);
+            tc::tma_load_2d(tc::smem_u32(packed + g * kPkBytes), &tm_w, pk, (kb_begin + kr) * 8, tp * kBM);
+          }
           if (load_p) { if (tma_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM); }
           else if (tma_q) tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
         }
@@ -481,6 +510,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
             uint8_t* sp = tiles + stage_i * kStageBytes;
             tc::mbar_arrive_expect_tx(full, tx_bytes);
             const int x = kb * kXPerBlock;
+            if (AWQ) {
+              const uint32_t pk = tc::smem_u32(&bar_pk[stage_i]);
+              tc::mbar_arrive_expect_tx(pk, pk_bytes);
+              tc::tma_load_2d(tc::smem_u32(packed + stage_i * kPkBytes), &tm_w, pk, kb * 8, tp * kBM);
+            }
             if (tma_p) tc::tma_load_2d(tc::smem_u32(sp), &tm_p, full, x, tp * kBM);
             if (tma_q) tc::tma_load_2d(tc::smem_u32(sp + kBM * kRowBytes), &tm_q, full, x, tq * BN);
             ++issued;
@@ -498,6 +532,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           const uint64_t t0 = tc::global_timer_ns();
           while (!tc::mbar_try_wait(tc::smem_u32(&bar_full[s]), ph) &&
                  tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
+          if (AWQ)
+            while (!tc::mbar_try_wait(tc::smem_u32(&bar_pk[s]), ph) && tc::global_timer_ns() - t0 < tc::kWaitLimitNs) {}
         }
       }
     }
@@ -539,53 +575,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     }
   } else if (AWQ && warp >= 6) {
     // ------------------------------- AWQ weight producer -------------------------
-    // Thread t fills rows t (and t + 128 of a 256-row tile) of the weight tile of every stage: eight
-    // packed words (64 values of K) -> eight 16-byte chunks of fp16, stored at the 128-byte-swizzle
-    // positions a TMA load would have used, then made visible to the tensor core (async proxy) before
-    // the warp's arrival.  The packed words of the next kDepth K blocks are already in registers when a
-    // block is dequantized (a load from L2 takes longer than the tensor core needs for a block).
-    constexpr int kRpt = BN > kBM ? BN / kBM : 1;      // rows per thread (two for 256-row weight tiles)
+    // 256 threads expand the packed 4-bit tile of every stage (delivered by TMA: 32 bytes = 64 values
+    // of K per weight row, 128 rows) into the stage's fp16 weight tile: a thread owns half a row --
+    // four packed words (eight values of K each) -> four 16-byte chunks of fp16, stored at the
+    // 128-byte-swizzle positions a TMA load of fp16 weights would have used, then made visible to the
+    // tensor core (async proxy) before the warp's arrival.  Two warps share a
+    // scheduler so that one's arithmetic hides the other's latencies.  The {scale, zero} pair of the
+    // row's quantization group is the only thing read from global memory here, kDepth blocks ahead.
     constexpr int kDepth = 4;
     const int t = (int)threadIdx.x - 6 * 32;
-    const int rpt = prm.swap ? 1 : kRpt;
-    const int w_off = prm.swap ? 0 : kBM * kRowBytes;  // offset of the weight tile inside a stage
-    const int n_limit = prm.N;
-    const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
-    const int total = my_tiles * kb_count;             // K blocks this CTA consumes, in ring order
-    uint32_t words[kDepth][kRpt][8];
-    uint32_t szv[kDepth][kRpt][2];                     // {scale, -(1024 + zero)} of words 0-3 and of words 4-7
-    auto fetch = [&](int q, uint32_t (&w)[kRpt][8], uint32_t (&z)[kRpt][2]) {
-      const int tile = first_tile + (q / kb_count) * tile_step, it = q % kb_count;
-      const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
-      int kr = it + (tp * 5 + tq * 3) % kb_count;      // the producer's K rotation
-      if (kr >= kb_count) kr -= kb_count;
-      const int kb = kb_begin + kr;                    // words 8 kb .. 8 kb + 7 of a row
-      const int n0 = prm.swap ? tp * kBM : tq * BN;
-#pragma unroll
-      for (int r = 0; r < kRpt; ++r) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w[r][j] = 0u;
-        z[r][0] = z[r][1] = 0u;
-        const int n = n0 + t + r * kBM;
-        if (r < rpt && q < total && n < n_limit) {
-          const uint32_t* src = prm.awq_w + (int64_t)n * prm.awq_kw + kb * 8;
-          if (kb * 8 + 8 <= prm.awq_kw) {
-            const uint4 a = ldg_stream_16B(src), c = ldg_stream_16B(src + 4);
-            w[r][0] = a.x; w[r][1] = a.y; w[r][2] = a.z; w[r][3] = a.w;
-            w[r][4] = c.x; w[r][5] = c.y; w[r][6] = c.z; w[r][7] = c.w;
-          } else {                                     // K ends inside this block: the rest stays zero
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (kb * 8 + j < prm.awq_kw) w[r][j] = src[j];
-          }
-          const uint32_t* zs = prm.awq_sz + (int64_t)n * prm.awq_kg;
-          z[r][0] = __ldg(zs + (kb * 64) / prm.awq_g);
-          if (kb * 8 + 4 < prm.awq_kw) z[r][1] = __ldg(zs + (kb * 64 + 32) / prm.awq_g);
-        }
+    const int rr = t & (kBM - 1);                      // my row of the 128-row weight tile
+    const int j0 = 4 * (t >> 7);                       // my four of the row's eight words
+    // prefetch cursor of the scale / zero pairs: walks the (tile, K block) sequence kDepth blocks ahead
+    int pf_tile = first_tile, pf_it = 0, pf_rot = 0;
+    const uint32_t* pf_z = nullptr;                    // my row's scale-zero pairs in the cursor's tile
+    auto pf_enter_tile = [&]() {
+      pf_z = nullptr;
+      if (pf_tile >= num_tiles) return;
+      const int tq = pf_tile % prm.tiles_q, tp = pf_tile / prm.tiles_q;
+      pf_rot = (tp * 5 + tq * 3) % kb_count;           // the TMA producer's K rotation
+      const int n = tp * kBM + rr;
+      if (n < prm.N) pf_z = prm.awq_sz + (int64_t)n * prm.awq_kg;
+    };
+    uint32_t szv[kDepth];                              // {scale, -(1024 + zero)} of my 32 values (groups of >= 32 values)
+    auto fetch = [&](uint32_t& z) {
+      z = 0u;                                          // scale 0: rows outside the matrix and values beyond K dequantize to 0
+      if (pf_z != nullptr) {
+        int kr = pf_it + pf_rot;
+        if (kr >= kb_count) kr -= kb_count;
+        const int wi = (kb_begin + kr) * 8 + j0;       // my first word of this K block
+        if (wi < prm.awq_kw) z = __ldg(pf_z + (wi * 8) / prm.awq_g);
+      }
+      if (++pf_it == kb_count) {                       // advance the cursor
+        pf_it = 0;
+        pf_tile += tile_step;
+        pf_enter_tile();
       }
     };
+    pf_enter_tile();
 #pragma unroll
-    for (int d = 0; d < kDepth; ++d) fetch(d, words[d], szv[d]);
+    for (int d = 0; d < kDepth; ++d) fetch(szv[d]);
+    const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
+    const int total = my_tiles * kb_count;             // K blocks this CTA consumes, in ring order
     int stage_i = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -593,34 +624,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
 #pragma unroll
       for (int d = 0; d < kDepth; ++d) {
         if (q0 + d >= total || !ok) continue;
-        tc::mbar_wait_or_flag(tc::smem_u32(&bar_empty[stage_i]), phase ^ 1u, abort_u32);
+        // the packed tile has landed; the TMA thread requested it only after the stage's previous
+        // contents had been consumed, so the fp16 tile may be overwritten as well
+        tc::mbar_wait_or_flag(tc::smem_u32(&bar_pk[stage_i]), phase, abort_u32);
         if (*abort) { ok = false; continue; }
-        uint8_t* wt = tiles + stage_i * kStageBytes + w_off;
+        {
+          const uint4 a = *reinterpret_cast<const uint4*>(packed + stage_i * kPkBytes + rr * kPackedRowBytes + j0 * 4);
+          uint4* dst = reinterpret_cast<uint4*>(tiles + stage_i * kStageBytes + rr * kRowBytes);
+          const uint32_t words[4] = {a.x, a.y, a.z, a.w};
+          const __half2 sz = *reinterpret_cast<const __half2*>(&szv[d]);
+          const __half2 negz = __half2half2(__high2half(sz)), sc = __half2half2(__low2half(sz));
 #pragma unroll
-        for (int r = 0; r < kRpt; ++r) {
-          if (r >= rpt) continue;
-          const int rr = t + r * kBM;
-          uint4* dst = reinterpret_cast<uint4*>(wt + rr * kRowBytes);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            // words of a row beyond K or N were fetched as zero with scale 0: (1024 + 0 - 0) * 0 = 0
-            const __half2 sz = *reinterpret_cast<const __half2*>(&szv[d][r][j >> 2]);
-            const __half2 negz = __half2half2(__high2half(sz)), sc = __half2half2(__low2half(sz));
+          for (int j = 0; j < 4; ++j) {
             uint32_t o[4];
 #pragma unroll
             for (int p4 = 0; p4 < 4; ++p4) {
-              uint32_t h = ((words[d][r][j] >> (4 * p4)) & 0x000F000Fu) | 0x64006400u;   // {1024 + v[2p], 1024 + v[2p+1]}
+              uint32_t h = ((words[j] >> (4 * p4)) & 0x000F000Fu) | 0x64006400u;         // {1024 + v[2p], 1024 + v[2p+1]}
               const __half2 v2 = __hmul2(__hadd2(*reinterpret_cast<__half2*>(&h), negz), sc);
               o[p4] = *reinterpret_cast<const uint32_t*>(&v2);
             }
-            dst[j ^ (rr & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[(j0 + j) ^ (rr & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> tensor-core reads
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(tc::smem_u32(&bar_full[stage_i]));
         if (++stage_i == kStages) { stage_i = 0; phase ^= 1u; }
-        fetch(q0 + d + kDepth, words[d], szv[d]);      // refill the slot for kDepth blocks ahead
+        fetch(szv[d]);                                 // refill the slot for kDepth blocks ahead
       }
     }
   } else {
@@ -687,7 +717,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     uint32_t* send = reinterpret_cast<uint32_t*>(tiles + BN * kBM * 4);
     const bool own_healthy = abort_flag == 0;          // own MMAs finished (epilogue warps waited for them)
     const int quad = warp & 3, et = quad * 32 + lane;
-    const bool epi_warp = warp >= 2 && warp < 6;       // (AWQ mode has four more warps behind them)
+    const bool epi_warp = warp >= 2 && warp < 6;       // (AWQ mode has more warps behind them)
     const int tq = first_tile % prm.tiles_q, tp = first_tile / prm.tiles_q;
     const EpiConsts& ec = ec_split;                    // q_scale / q_bias cover only the columns this CTA owns
     if (epi_warp && own_healthy) {
@@ -839,12 +869,27 @@ int make_operand_map(CUtensorMap* map, const void* base, int elt_bytes, int64_t 
   return LLMQRT_OK;
 }
 
+// Packed 4-bit weights as a 2-D uint32 matrix [rows, words] (row-major); box = 8 words x box_rows, no swizzle.
+int make_packed_map(CUtensorMap* map, const void* base, int64_t rows, int64_t words, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)words, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(words * 4)};
+  cuuint32_t box[2] = {8, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled (packed weights) failed with code %d", (int)r);
+  return LLMQRT_OK;
+}
+
 template <int KIND, int BN, bool AWQ = false>
 cudaLaunchConfig_t make_config(int grid, int cluster, cudaStream_t st, cudaLaunchAttribute* attr) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
   cfg.blockDim = dim3(AWQ ? kThreadsAwq : kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem_bytes<BN>();
+  cfg.dynamicSmemBytes = smem_bytes_of<BN, AWQ>();
   cfg.stream = st;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)cluster;
@@ -872,7 +917,7 @@ int max_active_clusters(int cluster) {
   if (it != cache.end()) return it->second;
   auto kern = gemm_tc_kernel<KIND, BN, AWQ>;
   int n = 0;
-  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>()) == LLMQRT_OK) {
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes_of<BN, AWQ>()) == LLMQRT_OK) {
     cudaLaunchAttribute attr[2];
     cudaLaunchConfig_t cfg = make_config<KIND, BN, AWQ>(cluster, cluster, nullptr, attr);
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
@@ -885,9 +930,9 @@ int max_active_clusters(int cluster) {
 }
 
 template <int KIND, int BN, bool AWQ = false>
-int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaStream_t st) {
+int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& tm_w, TcParams prm, cudaStream_t st) {
   auto kern = gemm_tc_kernel<KIND, BN, AWQ>;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes<BN>())) return rc;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes_of<BN, AWQ>())) return rc;
   const int sms = sm_count();
   const int tiles = prm.tiles_p * prm.tiles_q;
   int splits = 1;
@@ -909,17 +954,18 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, TcParams prm, cudaS
   const int grid = splits > 1 ? tiles * splits : (tiles < sms ? tiles : sms);
   cudaLaunchAttribute attr[2];
   cudaLaunchConfig_t cfg = make_config<KIND, BN, AWQ>(grid, splits, st, attr);
-  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_p, tm_q, prm));
+  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_p, tm_q, tm_w, prm));
   return check_launch("gemm_tc");
 }
 
 template <int KIND, bool AWQ = false>
-int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const TcParams& prm, cudaStream_t st) {
+int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& tm_w, const TcParams& prm,
+              cudaStream_t st) {
   switch (bn) {
-    case 32: return launch<KIND, 32, AWQ>(tm_p, tm_q, prm, st);
-    case 64: return launch<KIND, 64, AWQ>(tm_p, tm_q, prm, st);
-    case 128: return launch<KIND, 128, AWQ>(tm_p, tm_q, prm, st);
-    default: return launch<KIND, 256, AWQ>(tm_p, tm_q, prm, st);
+    case 32: return launch<KIND, 32, AWQ>(tm_p, tm_q, tm_w, prm, st);
+    case 64: return launch<KIND, 64, AWQ>(tm_p, tm_q, tm_w, prm, st);
+    case 128: return launch<KIND, 128, AWQ>(tm_p, tm_q, tm_w, prm, st);
+    default: return launch<KIND, 256, AWQ>(tm_p, tm_q, tm_w, prm, st);
   }
 }
 
@@ -929,8 +975,9 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
             const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w, const AwqOperand* awq) {
   const int elt = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
   if (awq) {                                           // W is produced in shared memory from the packed layer
-    LLMQRT_REQUIRE(kind == KIND_F16 && awq->wq_t && awq->sz_t && awq->G > 0 && K % 8 == 0 && K % awq->G == 0 &&
-                   awq->G % 8 == 0, "tcgen05 awq gemm: fp16 activations, K and group size multiples of 8");
+    LLMQRT_REQUIRE(kind == KIND_F16 && awq->wq_t && awq->sz_t && awq->G > 0 && K % 32 == 0 && K % awq->G == 0 &&
+                   awq->G % 32 == 0 && (reinterpret_cast<uintptr_t>(awq->wq_t) & 15) == 0,
+                   "tcgen05 awq gemm: fp16 activations, K and group size multiples of 32, 16-byte aligned packed weights");
     W = A;                                             // placeholder for the unused tensor map
     ldw = lda;
     static_w = false;
@@ -961,6 +1008,14 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   int bn;
   if (prm.swap) bn = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
   else bn = N <= 128 ? 128 : 256;
+  if (awq && !prm.swap) {
+    // AWQ with many tokens: the weights stay the 128-lane operand and the tokens come in tiles of 256.
+    // A dequantized weight tile (the expensive operand: it is produced by arithmetic, not by a copy)
+    // then serves 256 tokens instead of 128, halving the dequantization work per multiply; and the
+    // dequantizing warps only ever see 128-row weight tiles.
+    prm.swap = 1;
+    bn = 256;
+  }
   prm.rows_p = prm.swap ? (int)N : (int)M;
   prm.rows_q = prm.swap ? (int)M : (int)N;
   prm.k_blocks = (int)ceil_div(K * elt, kRowBytes);
@@ -989,11 +1044,14 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
     prm.awq_kw = (int)(K / 8);
     prm.awq_kg = (int)(K / awq->G);
     prm.awq_g = (int)awq->G;
-    return launch_bn<tc::MMA_F16, true>(bn, tm_p, tm_q, prm, st);
+    // packed words as a 2-D uint32 matrix [N, K / 8]; box = the 8 words of a K block x the tile's weight rows
+    CUtensorMap tm_w;
+    if (int rc = make_packed_map(&tm_w, awq->wq_t, N, K / 8, kBM)) return rc;
+    return launch_bn<tc::MMA_F16, true>(bn, tm_p, tm_q, tm_w, prm, st);
   }
-  if (mk == tc::MMA_I8) return launch_bn<tc::MMA_I8>(bn, tm_p, tm_q, prm, st);
-  if (mk == tc::MMA_F8) return launch_bn<tc::MMA_F8>(bn, tm_p, tm_q, prm, st);
-  return launch_bn<tc::MMA_F16>(bn, tm_p, tm_q, prm, st);
+  if (mk == tc::MMA_I8) return launch_bn<tc::MMA_I8>(bn, tm_p, tm_q, tm_p, prm, st);
+  if (mk == tc::MMA_F8) return launch_bn<tc::MMA_F8>(bn, tm_p, tm_q, tm_p, prm, st);
+  return launch_bn<tc::MMA_F16>(bn, tm_p, tm_q, tm_p, prm, st);
 }
 
 }  // namespace llmqrt
