@@ -383,8 +383,10 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
   // out_q (only passed when this block holds the sequence's WHOLE token row: one KV head, no splits):
   // the per-token int8 quantization of the row is done right here and the merge kernel is not launched.
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-  __shared__ uint16_t row_bits[8 * D];
-  __shared__ float red_amax[kWarps];
+  // (scratch behind the merge tile inside the idle rings: static shared memory would push two
+  // resident blocks over the next carve-out step and cost L1)
+  uint16_t* row_bits = reinterpret_cast<uint16_t*>(ring_all + kWarps * 8 * D * 4);
+  float* red_amax = reinterpret_cast<float*>(ring_all + kWarps * 8 * D * 4 + 8 * D * 2);
   float amax = 0.f;
   for (int i = tid; i < rep * D; i += kThreads) {
     const int hd = i / D, dd = i - hd * D;
@@ -510,7 +512,7 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   }
   const float scale = 1.0f / sqrtf((float)D);
   constexpr int smem = kWarps * kRing * 2 * 16 * D * 2;           // per-warp rings; also holds the 16 KiB merge tile
-  static_assert(smem >= kWarps * 8 * D * 4, "ring too small for the merge tile");
+  static_assert(smem >= kWarps * 8 * D * 4 + 8 * D * 2 + kWarps * 4, "ring too small for the merge tile and the quantization scratch");
   auto kern = attn_decode_kernel<BF16, D>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
   // One KV head and no splits (a tensor-parallel rank that holds a single KV head): the attention block
