@@ -322,6 +322,15 @@ def run_ours(args):
     def dev_step():
         state["tok"] = model.decode_step(state["tok"])
 
+    # Untimed ramp: a run of only a few steps would otherwise be measured while the GPU is still leaving
+    # its idle clocks (a 2-step run read 3x slower on every kernel).  At least half a second of steps.
+    t_ramp = time.perf_counter()
+    while time.perf_counter() - t_ramp < 0.5:
+        model.reset_position(args.prompt_len)
+        for _ in range(8):
+            dev_step()
+        torch.cuda.synchronize(dev)
+
     with ClockSampler(local) as clocks:
         block_secs = timed_blocks(dev_step)
     secs = statistics.median(block_secs)
