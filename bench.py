@@ -323,13 +323,13 @@ def run_ours(args):
         state["tok"] = model.decode_step(state["tok"])
 
     # Untimed ramp: a run of only a few steps would otherwise be measured while the GPU is still leaving
-    # its idle clocks (a 2-step run read 3x slower on every kernel).  At least half a second of steps.
-    t_ramp = time.perf_counter()
-    while time.perf_counter() - t_ramp < 0.5:
+    # its idle clocks (a 2-step run read 3x slower on every kernel).  A fixed number of steps (the same
+    # on every rank: the steps contain collectives), about 0.4 s on one GPU.
+    for _ in range(16):
         model.reset_position(args.prompt_len)
         for _ in range(8):
             dev_step()
-        torch.cuda.synchronize(dev)
+    torch.cuda.synchronize(dev)
 
     with ClockSampler(local) as clocks:
         block_secs = timed_blocks(dev_step)
