@@ -148,13 +148,11 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
                    const int32_t* __restrict__ seqlens, uint16_t* __restrict__ out, int Hq, int Hkv, int chunk,
                    int max_splits, int max_len, float scale, float softcap, float* __restrict__ part_o,
                    float* __restrict__ part_ml, DecodeAppend ap, int8_t* __restrict__ out_q,
-                   float* __restrict__ out_scale) {
+                   float* __restrict__ out_scale, int q_cluster) {
   constexpr int NJ = D / 32;          // 16-byte K chunks per lane (quad covers 64 B per step)
   constexpr int NH = D / 64;          // 16-byte V chunks per lane (8 lanes cover 128 B per step)
-  LLMQRT_TIMELINE_MARK(40);
   pdl_wait();
   pdl_trigger();
-  LLMQRT_TIMELINE_MARK(41);
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int rep = Hq / Hkv;
   // A length beyond the bound the grid and the partial slots were sized for (the host's max_seqlen,
@@ -380,8 +378,11 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
     }
   __syncthreads();
 
-  // out_q (only passed when this block holds the sequence's WHOLE token row: one KV head, no splits):
-  // the per-token int8 quantization of the row is done right here and the merge kernel is not launched.
+  // out_q (only passed without splits, when the blocks of the sequence's KV heads -- this one alone, or
+  // the q_cluster CTAs of this thread-block cluster -- hold the WHOLE token row between them): the
+  // per-token int8 quantization of the row is done right here and the merge kernel is not launched.
+  // The row's absolute maximum is the one thing the blocks exchange, through distributed shared memory.
+  __shared__ float cl_amax[8];                       // slot r: the maximum found by the cluster's CTA r
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   // (scratch behind the merge tile inside the idle rings: static shared memory would push two
   // resident blocks over the next carve-out step and cost L1)
@@ -429,13 +430,29 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
     amax = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) amax = fmaxf(amax, red_amax[w]);
+    if (q_cluster > 1) {
+      // every CTA writes its maximum into its slot in EVERY CTA of the cluster (a dedicated static
+      // array: the rings of a CTA that is still streaming keys must not be written), then one cluster
+      // barrier (release / acquire) and each CTA reads its own copy -- nobody reads remote memory
+      // afterwards, so a CTA may leave as soon as it is through the barrier
+      uint32_t my_rank;
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my_rank));
+      if (tid < q_cluster) {
+        uint32_t remote;
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_amax[my_rank]);
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)tid));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(amax) : "memory");
+      }
+      asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+      for (int r = 0; r < q_cluster; ++r) amax = fmaxf(amax, cl_amax[r]);
+    }
     float sc = round_to<T>(fmaxf(amax, 1e-5f));
     sc = round_to<T>(__fmul_rn(sc, 1.0f / 127.0f));
-    if (tid == 0) out_scale[b] = sc;
+    if (tid == 0 && hkv == 0) out_scale[b] = sc;
     for (int i = tid; i < rep * D; i += kThreads) {
       float v = rintf(round_to<T>(__fdiv_rn(bits_to_f32<BF16>(row_bits[i]), sc)));
       v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
-      out_q[(int64_t)b * Hq * D + i] = (int8_t)(int)v;         // Hkv == 1: the block's rows are the whole token row
+      out_q[((int64_t)b * Hq + hkv * rep) * D + i] = (int8_t)(int)v;     // this block's heads of the token row
     }
   }
 }
@@ -452,9 +469,7 @@ attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __rest
                            int8_t* __restrict__ out_q, float* __restrict__ out_scale) {
   extern __shared__ __align__(16) uint8_t row_raw[];
   __shared__ float red[32];
-  LLMQRT_TIMELINE_MARK(50);
   pdl_trigger_then_wait();
-  LLMQRT_TIMELINE_MARK(51);
   const int b = blockIdx.x;
   const int L = min(seqlens[b], max_len);          // same clamp as the main kernel
   const int n_splits = (L + chunk - 1) / chunk;
@@ -476,6 +491,16 @@ __global__ void kv_append_kernel(uint4* __restrict__ k_cache, uint4* __restrict_
     k_cache[dst + i] = k[src + i];
     v_cache[dst + i] = v[src + i];
   }
+}
+
+// Quantization inside the attention kernel is used unless the environment variable
+// LLMQRT_ATTN_FUSED_QUANT is "0" (then the merge kernel quantizes).
+bool quant_fused_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("LLMQRT_ATTN_FUSED_QUANT");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 template <bool BF16, int D>
@@ -515,15 +540,19 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   static_assert(smem >= kWarps * 8 * D * 4 + 8 * D * 2 + kWarps * 4, "ring too small for the merge tile and the quantization scratch");
   auto kern = attn_decode_kernel<BF16, D>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
-  // One KV head and no splits (a tensor-parallel rank that holds a single KV head): the attention block
-  // of a sequence produces the whole token row and quantizes it itself -- one kernel less per layer.
-  const bool quant_in_kernel = out_q != nullptr && Hkv == 1 && max_splits == 1 && Hq <= 8;
+  // No splits: the attention blocks of a sequence produce the whole token row and quantize it
+  // themselves -- one kernel less per layer.
+  // Several KV heads: the blocks of one sequence form a thread-block cluster (at most 8 CTAs) and
+  // exchange the row maximum through distributed shared memory.
+  const bool quant_in_kernel = out_q != nullptr && Hkv <= 8 && max_splits == 1 && Hq / Hkv <= 8 && quant_fused_enabled();
+  const int q_cluster = quant_in_kernel ? Hkv : 1;
   const bool need_merge = max_splits > 1 || (out_q != nullptr && !quant_in_kernel);
-  if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, 1,
+  if (int rc = launch_chained(kern, dim3(max_splits, Hkv, B), dim3(kThreads), smem, st, dim3(1, (unsigned)q_cluster, 1),
                               reinterpret_cast<const uint16_t*>(q), qbs, reinterpret_cast<const uint16_t*>(kc),
                               reinterpret_cast<const uint16_t*>(vc), bs, rs, seqlens, reinterpret_cast<uint16_t*>(out),
                               Hq, Hkv, chunk, max_splits, max_seqlen, scale, softcap, part_o, part_ml, ap,
-                              quant_in_kernel ? out_q : (int8_t*)nullptr, quant_in_kernel ? out_scale : (float*)nullptr))
+                              quant_in_kernel ? out_q : (int8_t*)nullptr, quant_in_kernel ? out_scale : (float*)nullptr,
+                              q_cluster))
     return rc;
   if (int rc = check_launch("attn_decode")) return rc;
   if (need_merge) {
@@ -625,4 +654,3 @@ int llmqrt_attn_decode_append(const void* q, int64_t q_batch_stride, const void*
 
 }  // extern "C"
 
-LLMQRT_TIMELINE_DUMP(attn)

@@ -71,62 +71,8 @@ __device__ __forceinline__ void pdl_trigger_then_wait() {
 }
 bool pdl_enabled();   // capi.cu: on unless the environment variable LLMQRT_PDL is "0"
 
-// ----------------------------------------------------------------------------------------------
-// In-situ timeline (build with -DLLMQRT_TIMELINE): thread 0 of block 0 of an instrumented kernel
-// appends (global-timer ns, low 8 bits replaced by an event id) to a per-source-file device buffer;
-// LLMQRT_TIMELINE_DUMP(name) defines `llmqrt_timeline_<name>(out, capacity, reset)` that copies the
-// buffer to the host.  Successive "ready" marks (taken right after the dependency wait) bound each
-// kernel's duration inside a chained or graph-replayed sequence without a profiler.
-// ----------------------------------------------------------------------------------------------
-#ifdef LLMQRT_TIMELINE
-constexpr unsigned kTimelineCap = 1u << 15;
-struct TimelineBuf { unsigned n; unsigned pad; unsigned long long ev[kTimelineCap]; };
-static __device__ TimelineBuf g_timeline;
-__device__ __forceinline__ void timeline_mark(unsigned id) {
-  if ((blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const unsigned i = atomicAdd(&g_timeline.n, 1u);
-    if (i < kTimelineCap) g_timeline.ev[i] = (t & ~0x3full) | (id & 0x3fu);
-  }
-}
-// Appends marks taken as SM-clock readings (clock64(), 0 = not taken): they are placed on the global
-// timer axis relative to "now", assuming 1.9 SM cycles per ns.  One thread, once per block.
-__device__ __forceinline__ void timeline_flush(const long long* clk, const unsigned* ids, int n) {
-  unsigned long long g1;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
-  const long long c1 = clock64();
-  int valid = 0;
-  for (int i = 0; i < n; ++i) valid += clk[i] != 0;
-  unsigned at = atomicAdd(&g_timeline.n, (unsigned)valid);
-  for (int i = 0; i < n; ++i) {
-    if (clk[i] == 0) continue;
-    const unsigned long long t = g1 - (unsigned long long)((c1 - clk[i]) * 10 / 19);
-    if (at < kTimelineCap) g_timeline.ev[at] = (t & ~0x3full) | (ids[i] & 0x3fu);
-    ++at;
-  }
-}
-#define LLMQRT_TIMELINE_MARK(id) ::llmqrt::timeline_mark(id)
-#define LLMQRT_TIMELINE_DUMP(name)                                                                          \
-  extern "C" int llmqrt_timeline_##name(unsigned long long* out, int capacity, int reset) {                \
-    static ::llmqrt::TimelineBuf host;                                                                      \
-    if (cudaMemcpyFromSymbol(&host, ::llmqrt::g_timeline, sizeof(host)) != cudaSuccess) return -1;          \
-    int n = (int)(host.n < ::llmqrt::kTimelineCap ? host.n : ::llmqrt::kTimelineCap);                       \
-    if (n > capacity) n = capacity;                                                                         \
-    for (int i = 0; i < n; ++i) out[i] = host.ev[i];                                                        \
-    if (reset) {                                                                                            \
-      const unsigned zero = 0;                                                                              \
-      if (cudaMemcpyToSymbol(::llmqrt::g_timeline, &zero, sizeof(zero)) != cudaSuccess) return -1;          \
-    }                                                                                                       \
-    return n;                                                                                               \
-  }
-#else
-#define LLMQRT_TIMELINE_MARK(id) do {} while (0)
-#define LLMQRT_TIMELINE_DUMP(name)
-#endif
-
 template <typename... KArgs, typename... Args>
-inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_x,
+inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, dim3 cluster,
                           Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
@@ -135,11 +81,11 @@ inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  if (cluster_x > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = (unsigned)cluster_x;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = 1;
+    attr[n].val.clusterDim.x = cluster.x;
+    attr[n].val.clusterDim.y = cluster.y;
+    attr[n].val.clusterDim.z = cluster.z;
     ++n;
   }
   if (pdl_enabled()) {
@@ -151,6 +97,11 @@ inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
   cfg.numAttrs = n;
   LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
   return LLMQRT_OK;
+}
+template <typename... KArgs, typename... Args>
+inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_x,
+                          Args... args) {
+  return launch_chained(kern, grid, block, smem, st, dim3((unsigned)(cluster_x > 1 ? cluster_x : 1), 1, 1), args...);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -318,23 +318,6 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
   }
 }
 
-// Optional stage timestamps of block 0 (build with -DLLMQRT_TIMELINE): events 52 + slot of the
-// in-situ timeline, recorded by whichever thread reaches the stage.
-#ifdef LLMQRT_TIMELINE
-// Marks are SM-clock readings parked in shared memory (a few cycles each); thread 0 converts them to
-// global-timer time and appends them to the timeline when the block tears down.
-#define TC_TRACE(slot)                                                         \
-  do {                                                                         \
-    if (blockIdx.x == 0) tr_clk[slot] = clock64();                             \
-  } while (0)
-#else
-#define TC_TRACE(slot) do {} while (0)
-#endif
-
-#ifdef LLMQRT_TIMELINE
-__device__ unsigned long long g_last_done;   // latest exit time over the blocks of the launch in flight
-#endif
-
 template <int KIND, int BN, bool AWQ = false>
 __global__ void __launch_bounds__(AWQ ? kThreadsAwq : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
@@ -372,17 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   const int S = prm.splits;
   const int my_split = S > 1 ? (int)cluster_ctarank() : 0;
 
-#ifdef LLMQRT_TIMELINE
-  __shared__ long long tr_clk[16];     // slots 0-10: stages below; 11 enter, 12 dependency met, 13 done
-  __shared__ unsigned long long tr_prev_last_done;   // when the last block of the previous launch of this kernel left
-#endif
   if (threadIdx.x == 0) {
-#ifdef LLMQRT_TIMELINE
-    for (int i = 0; i < 16; ++i) tr_clk[i] = 0;
-    if (blockIdx.x == 0) tr_prev_last_done = atomicExch(&g_last_done, 0ull);
-#endif
-    TC_TRACE(11);
-    TC_TRACE(0);
     abort_flag = 0;
     cluster_abort = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -408,7 +381,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
-  if (threadIdx.x == 0) TC_TRACE(1);
   // Everything above touched only shared and tensor memory; from here on global memory is read.
   // The producer thread waits later: it first requests weight tiles, which the preceding kernel of
   // the stream does not write.
@@ -451,7 +423,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       const uint32_t pk_bytes = (uint32_t)kPackedBytes;
       if (!early_w) {
         pdl_wait();
-        TC_TRACE(12);
         pdl_trigger();
       }
       const int pre = first_tile < num_tiles ? min(kStages, kb_count) : 0;
@@ -479,7 +450,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           // ring already keeps more bytes in flight than HBM needs, and the activation loads then
           // queue behind the prefetches.)
           pdl_wait();
-          TC_TRACE(12);
           pdl_trigger();
         }
       }
@@ -553,7 +523,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           // No result and no tcgen05 fence here: the tiles were written by TMA, whose completion on
           // the barrier orders them before MMAs issued after the wait; the flag is checked per tile.
           tc::mbar_wait_or_flag(tc::smem_u32(&bar_full[stage_i]), phase, abort_u32);
-          if (it == 0) TC_TRACE(2);
           const uint32_t sp = tc::smem_u32(tiles + stage_i * kStageBytes);
           const uint64_t dp = tc::smem_desc_k_major_sw128(sp);
           const uint64_t dq = tc::smem_desc_k_major_sw128(sp + kBM * kRowBytes);
@@ -568,7 +537,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         }
         if (*abort) { ok = false; break; }
         tc::mma_commit(tc::smem_u32(&bar_acc_full[buf]));        // accumulator complete
-        TC_TRACE(3);
         acc_phase[buf] ^= 1u;
         buf ^= 1;
       }
@@ -677,7 +645,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       if (tc::named_barrier_or(2, 128, failed)) break;
       tc::fence_after_sync();
       acc_phase[buf] ^= 1u;
-      if (threadIdx.x == 64) TC_TRACE(4);
       if (S > 1) break;                                // split mode: the reduce-scatter below takes over
 
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
@@ -736,7 +703,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           for (int jj = 0; jj < 8; ++jj) send[(c0 + 8 * q + jj) * kBM + et] = r[q][jj];
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> bulk-copy reads
-      if (threadIdx.x == 64) TC_TRACE(7);
       if (threadIdx.x == 64) tc::mbar_arrive_expect_tx(tc::smem_u32(&bar_reduce), slice_bytes * (uint32_t)S);
     }
     // A CTA whose waits ran out tells every CTA of the cluster before the barrier, and then ALL of
@@ -760,7 +726,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
                          tc::smem_u32(send) + (uint32_t)o * slice_bytes, slice_bytes, tc::smem_u32(&bar_reduce),
                          (uint32_t)o);
     }
-    if (threadIdx.x == 64) TC_TRACE(8);
     // Once every slice addressed to this CTA has landed, the peers' `send` buffers are no longer
     // being read on its behalf: tell each of them.  A CTA leaves once all S owners have said so, which
     // by then happened during its own epilogue -- no cluster barrier at the end.  Done by the otherwise
@@ -774,7 +739,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       const bool failed = !healthy || !tc::mbar_wait(tc::smem_u32(&bar_reduce), 0u, abort);
       reduce_ok = !tc::named_barrier_or(2, 128, failed);
     }
-    if (threadIdx.x == 64) TC_TRACE(9);
     if (epi_warp && reduce_ok) {
       const AccT* rbuf = reinterpret_cast<const AccT*>(tiles);
 #pragma unroll 1
@@ -805,31 +769,228 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     }
     // Nobody leaves while a peer may still be copying out of its `send` buffer (bounded: a peer that
     // failed never reports, and the block then gives up with the abort flag raised).
-    if (threadIdx.x == 64) TC_TRACE(10);
     if (threadIdx.x == 64 && healthy) tc::mbar_wait(tc::smem_u32(&bar_release), 0u, abort);
   }
   }
 
   // ------------------------------- teardown ---------------------------------------
-  if (threadIdx.x == 64) TC_TRACE(5);
   tc::fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) TC_TRACE(6);
-#ifdef LLMQRT_TIMELINE
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    tr_clk[13] = clock64();
-    const unsigned ids[16] = {52, 53, 54, 55, 56, 57, 58, 59, 60, 61, 62, 1, 2, 3, 0, 0};
-    timeline_flush(tr_clk, ids, 14);
-    if (tr_prev_last_done) {
-      const unsigned at = atomicAdd(&g_timeline.n, 1u);
-      if (at < kTimelineCap) g_timeline.ev[at] = (tr_prev_last_done & ~0x3full) | 4u;
-    }
-  }
-  if (threadIdx.x == 0) atomicMax(&g_last_done, tc::global_timer_ns());
-#endif
   if (warp == 1) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_flag && prm.status) *prm.status = 1u;
+}
+
+
+// ---- two-CTA kernel for prefill-sized problems -------------------------------------------------
+// Tokens are the 128-lane operand.  The two CTAs of a cluster compute one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2 (M = 256, N = 256): each CTA stages ITS 128 token rows and ITS 128 of the
+// tile's 256 weight rows, 32 KiB per K block of 128 bytes instead of the 48 KiB a lone CTA needs for a
+// 128 x 256 tile, and each MMA reads 8 KiB instead of 12 KiB of a CTA's shared memory per 128 x 256 x 32
+// multiply -- the shared-memory operand feed, not the tensor pipe, is what bounds the single-CTA form.
+// Each CTA's tensor memory receives its 128 accumulator rows (2 x 256 columns, double buffered).
+//   producer (warp 0, both CTAs): TMA loads whose bytes are counted on the LEADER's `full` barrier
+//   MMA issuer (warp 1, leader only): 4 MMAs per stage, commits fan out to both CTAs' barriers
+//   epilogue (warps 2-5, both CTAs): TMEM -> registers -> scales / bias -> 128-byte-swizzled staging
+//     tile -> TMA store (clipped at the matrix edge by the tensor map)
+constexpr int kPairBN = 256;
+constexpr int kPairHalfB = kPairBN / 2;
+constexpr int kPairStageBytes = (kBM + kPairHalfB) * kRowBytes;         // 32 KiB
+constexpr int kPairStages = 6;
+constexpr int kPairStoreBytes = kBM * 128;                             // output staging: 128 rows x 128 bytes
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairStoreBytes + 1024;
+constexpr uint32_t kPairTmemCols = 2 * kPairBN;
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                    const __grid_constant__ CUtensorMap tm_out, TcParams prm) {
+  using AccT = typename std::conditional<KIND == tc::MMA_I8, int, float>::type;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ostage = tiles + kPairStages * kPairStageBytes;
+  __shared__ __align__(8) uint64_t bar_full[kPairStages];      // used in the leader only
+  __shared__ __align__(8) uint64_t bar_empty[kPairStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];           // used in the leader only: one arrival per CTA
+  __shared__ __align__(16) float q_scale[kPairBN];
+  __shared__ __align__(16) float q_bias[kPairBN];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort = &abort_flag;
+  const uint32_t abort_u32 = tc::smem_u32(&abort_flag);
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      tc::mbar_init(tc::smem_u32(&bar_full[s]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(tc::smem_u32(&bar_acc_full[b]), 1);
+      tc::mbar_init(tc::smem_u32(&bar_acc_empty[b]), 2);
+    }
+    tc::mbar_fence_init();
+    tc::tma_prefetch_descriptor(&tm_a);
+    tc::tma_prefetch_descriptor(&tm_w);
+    tc::tma_prefetch_descriptor(&tm_out);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc_pair(tc::smem_u32(&tmem_base_slot), kPairTmemCols);
+    tc::tmem_relinquish_pair();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                  // both CTAs' barriers exist before anything signals them
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();
+  pdl_trigger();
+
+  const int num_tiles = prm.tiles_p * prm.tiles_q;     // in units of 256 x 256
+  const int first_tile = (int)(blockIdx.x >> 1), tile_step = (int)(gridDim.x >> 1);
+  const int kb_count = prm.k_blocks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      constexpr int kXPerBlock = KIND == tc::MMA_F16 ? kRowBytes / 2 : kRowBytes;
+      const uint32_t full0 = tc::cluster_addr(tc::smem_u32(&bar_full[0]), 0u);   // the leader's barriers
+      int stage_i = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
+        const int row_a = tp * 2 * kBM + (int)rank * kBM, row_w = tq * kPairBN + (int)rank * kPairHalfB;
+        for (int it = 0; it < kb_count; ++it) {
+          tc::mbar_wait_or_flag(tc::smem_u32(&bar_empty[stage_i]), phase ^ 1u, abort_u32);
+          if (leader) tc::mbar_arrive_expect_tx(tc::smem_u32(&bar_full[stage_i]), 2u * kPairStageBytes);
+          const uint32_t full = full0 + (uint32_t)stage_i * 8u;
+          const uint32_t sp = tc::smem_u32(tiles + stage_i * kPairStageBytes);
+          tc::tma_load_2d_pair(sp, &tm_a, full, it * kXPerBlock, row_a);
+          tc::tma_load_2d_pair(sp + kBM * kRowBytes, &tm_w, full, it * kXPerBlock, row_w);
+          if (++stage_i == kPairStages) { stage_i = 0; phase ^= 1u; }
+        }
+        if (*abort) ok = false;
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      int stage_i = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int buf = 0;
+      for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
+        if (!tc::mbar_wait(tc::smem_u32(&bar_acc_empty[buf]), acc_phase[buf] ^ 1u, abort)) break;
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kPairBN);
+        for (int it = 0; it < kb_count; ++it) {
+          tc::mbar_wait_or_flag(tc::smem_u32(&bar_full[stage_i]), phase, abort_u32);
+          const uint32_t sp = tc::smem_u32(tiles + stage_i * kPairStageBytes);
+          const uint64_t da = tc::smem_desc_k_major_sw128(sp);
+          const uint64_t db = tc::smem_desc_k_major_sw128(sp + kBM * kRowBytes);
+#pragma unroll
+          for (int j = 0; j < kRowBytes / 32; ++j)
+            tc::mma_ss_pair<KIND>(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), prm.idesc,
+                                  (it > 0 || j > 0) ? 1u : 0u);
+          tc::mma_commit_pair(tc::smem_u32(&bar_empty[stage_i]));      // frees the stage in both CTAs
+          if (++stage_i == kPairStages) { stage_i = 0; phase ^= 1u; }
+        }
+        if (*abort) break;
+        tc::mma_commit_pair(tc::smem_u32(&bar_acc_full[buf]));          // accumulators complete in both CTAs
+        acc_phase[buf] ^= 1u;
+        buf ^= 1;
+      }
+    }
+  } else {
+    const int quad = warp & 3, et = quad * 32 + lane;
+    const bool issuer = threadIdx.x == 64;
+    const Epilogue& e = prm.epi;
+    const bool raw = e.mode == EPI_RAW;
+    const bool wide = raw || e.out_dtype == LLMQRT_F32;                 // 4-byte outputs: 32 columns per 128-byte row
+    const int cw = wide ? 32 : 64;
+    const float alpha = e.alpha_dev ? *e.alpha_dev : e.alpha;
+    const uint32_t acc_empty0 = tc::cluster_addr(tc::smem_u32(&bar_acc_empty[0]), 0u);
+    uint4* my_row = reinterpret_cast<uint4*>(ostage + et * 128);
+    const int sw = et & 7;
+    uint32_t acc_phase[2] = {0, 0};
+    int buf = 0;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
+      const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
+      const int row0 = tp * 2 * kBM + (int)rank * kBM;
+      epi_barrier();                                   // previous tile no longer reads q_scale / q_bias
+      const EpiConsts ec = epi_setup(prm, alpha, row0 + et, tq * kPairBN, kPairBN, et, q_scale, q_bias);
+      const bool failed = !tc::mbar_wait(tc::smem_u32(&bar_acc_full[buf]), acc_phase[buf], abort);
+      if (tc::named_barrier_or(2, 128, failed)) break;
+      tc::fence_after_sync();
+      acc_phase[buf] ^= 1u;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPairBN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPairBN; c0 += cw) {
+        const int col0 = tq * kPairBN + c0;
+        if (col0 >= prm.N) break;
+#pragma unroll 1
+        for (int h = 0; h * 32 < cw; ++h) {
+          uint32_t r[32];
+          tc::tmem_ld_32x32(taddr + (uint32_t)(c0 + 32 * h), r);
+          tc::tmem_ld_wait();
+          if (!raw) {
+            const float* qs = q_scale + c0 + 32 * h;
+            const float* qb = q_bias + c0 + 32 * h;
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              r[jj] = __float_as_uint(epi_value(ec, (float)acc_from_bits<AccT>(r[jj]), qs[jj], qb[jj], false));
+          }
+          if (h == 0) {
+            // the staging tile is free once the previous TMA store has read it
+            if (issuer) tc::tma_store_wait_read<0>();
+            epi_barrier();
+          }
+          if (wide) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) my_row[k ^ sw] = make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              my_row[(4 * h + k) ^ sw] =
+                  make_uint4(pack16(__uint_as_float(r[8 * k]), __uint_as_float(r[8 * k + 1]), e.out_dtype),
+                             pack16(__uint_as_float(r[8 * k + 2]), __uint_as_float(r[8 * k + 3]), e.out_dtype),
+                             pack16(__uint_as_float(r[8 * k + 4]), __uint_as_float(r[8 * k + 5]), e.out_dtype),
+                             pack16(__uint_as_float(r[8 * k + 6]), __uint_as_float(r[8 * k + 7]), e.out_dtype));
+          }
+        }
+        tc::fence_proxy_async_smem();                  // generic writes -> TMA store reads
+        tc::fence_before_sync();
+        epi_barrier();
+        if (issuer && row0 < prm.M) {
+          tc::tma_store_2d(&tm_out, tc::smem_u32(ostage), col0, row0);
+          tc::tma_store_commit();
+        }
+      }
+      // every thread's tensor-memory reads are done (barrier above): the buffer may be overwritten
+      if (issuer) tc::mbar_arrive_cluster(acc_empty0 + (uint32_t)buf * 8u);
+      buf ^= 1;
+    }
+    if (issuer) tc::tma_store_wait_all();
+  }
+
+  // ------------------------------- teardown ---------------------------------------
+  tc::fence_before_sync();
+  __syncthreads();
+  if (abort_flag) {
+    // a wait ran out: give copies that may still be in flight towards either CTA time to land
+    const uint64_t t0 = tc::global_timer_ns();
+    while (tc::global_timer_ns() - t0 < 100000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();                                  // nobody leaves while its peer may still signal it
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc_pair(tmem_base, kPairTmemCols);
   }
   if (threadIdx.x == 0 && abort_flag && prm.status) *prm.status = 1u;
 }
@@ -958,6 +1119,85 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& 
   return check_launch("gemm_tc");
 }
 
+// Output matrix [M, N] (ld elements between rows) for TMA stores out of a 128-byte-swizzled staging
+// tile: box = 128 bytes x 128 rows.
+int make_out_map(CUtensorMap* map, void* base, int elt_bytes, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * elt_bytes)};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elt_bytes), (cuuint32_t)kBM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, elt_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
+  return LLMQRT_OK;
+}
+
+// Clusters of two CTAs of the pair kernel that can be resident at once (cached per device).
+template <int KIND>
+int pair_max_clusters() {
+  static std::mutex mu;
+  static std::map<int, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(dev);
+  if (it != cache.end()) return it->second;
+  auto kern = gemm_tc_pair_kernel<KIND>;
+  int n = 0;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kPairSmemBytes) == LLMQRT_OK) {
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+  }
+  cache[dev] = n;
+  return n;
+}
+
+template <int KIND>
+int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_w, const CUtensorMap& tm_out, const TcParams& prm,
+                cudaStream_t st) {
+  auto kern = gemm_tc_pair_kernel<KIND>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kPairSmemBytes)) return rc;
+  int clusters = pair_max_clusters<KIND>();
+  if (clusters <= 0) return set_error(LLMQRT_ERR_CUDA, "tcgen05 pair gemm: no cluster of two CTAs fits on this device");
+  const int tiles = prm.tiles_p * prm.tiles_q;
+  if (clusters > tiles) clusters = tiles;
+  cudaLaunchAttribute attr[2];
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = st;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (pdl_enabled()) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, tm_out, prm));
+  return check_launch("gemm_tc_pair");
+}
+
 template <int KIND, bool AWQ = false>
 int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& tm_w, const TcParams& prm,
               cudaStream_t st) {
@@ -967,6 +1207,15 @@ int launch_bn(int bn, const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CU
     case 128: return launch<KIND, 128, AWQ>(tm_p, tm_q, tm_w, prm, st);
     default: return launch<KIND, 256, AWQ>(tm_p, tm_q, tm_w, prm, st);
   }
+}
+
+// The two-CTA kernel is used unless the environment variable LLMQRT_GEMM_PAIR is "0".
+bool pair_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("LLMQRT_GEMM_PAIR");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 }  // namespace
@@ -1030,6 +1279,26 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   else if (kind == KIND_F8_E5M2) { fmt_act = 1; }
   else if (kind == KIND_F16) { mk = tc::MMA_F16; }
   else if (kind == KIND_BF16) { mk = tc::MMA_F16; fmt_act = fmt_w = 1; }
+
+  // Prefill-sized problems whose 256-row pair tiles waste no more rows than 128-row tiles would: the
+  // two-CTA kernel.  Its TMA stores need a 16-byte aligned output with a 16-byte multiple row pitch.
+  {
+    const int es = (epi.mode == EPI_RAW || epi.out_dtype == LLMQRT_F32) ? 4 : 2;
+    const bool out_ok = (reinterpret_cast<uintptr_t>(epi.out) & 15) == 0 && (epi.ldo * es) % 16 == 0;
+    const bool rows_ok = M >= 2048 || ceil_div(M, (int64_t)256) * 256 == ceil_div(M, (int64_t)128) * 128;
+    if (!awq && !prm.swap && bn == 256 && M >= 512 && rows_ok && out_ok && pair_enabled()) {
+      prm.tiles_p = (int)ceil_div(M, (int64_t)(2 * kBM));
+      prm.tiles_q = (int)ceil_div(N, (int64_t)kPairBN);
+      prm.idesc = tc::instr_desc(c_fmt, fmt_act, fmt_w, 2 * kBM, kPairBN);
+      CUtensorMap tm_a, tm_w, tm_out;
+      if (int rc = make_operand_map(&tm_a, A, elt, M, K, lda, kBM)) return rc;
+      if (int rc = make_operand_map(&tm_w, W, elt, N, K, ldw, kPairHalfB)) return rc;
+      if (int rc = make_out_map(&tm_out, epi.out, es, M, N, epi.ldo)) return rc;
+      if (mk == tc::MMA_I8) return launch_pair<tc::MMA_I8>(tm_a, tm_w, tm_out, prm, st);
+      if (mk == tc::MMA_F8) return launch_pair<tc::MMA_F8>(tm_a, tm_w, tm_out, prm, st);
+      return launch_pair<tc::MMA_F16>(tm_a, tm_w, tm_out, prm, st);
+    }
+  }
   prm.idesc = tc::instr_desc(c_fmt, prm.swap ? fmt_w : fmt_act, prm.swap ? fmt_act : fmt_w, kBM, (uint32_t)bn);
 
   CUtensorMap tm_p, tm_q;
@@ -1056,4 +1325,3 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
 
 }  // namespace llmqrt
 
-LLMQRT_TIMELINE_DUMP(gemm)

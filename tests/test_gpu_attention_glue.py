@@ -224,14 +224,17 @@ def test_decode_append_on_a_full_cache_writes_nothing():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("Hq,lens,Smax", [(4, [1100, 1, 300, 0, 513], 1200), (3, [40, 7, 64], 64), (7, [200, 199], 256),
-                                           (4, [5000, 4097], 5100)])
-def test_decode_fused_quantization_single_kv_head(dtype, Hq, lens, Smax):
-    # one KV head (a tensor-parallel rank of 4 or 8): an unsplit sequence is quantized by the attention
-    # kernel itself, a split one by the merge kernel; both must be the per-token quantizer's bits
+@pytest.mark.parametrize("Hq,Hkv,lens,Smax", [(4, 1, [1100, 1, 300, 0, 513], 1200), (3, 1, [40, 7, 64], 64),
+                                               (7, 1, [200, 199], 256), (4, 1, [5000, 4097], 5100),
+                                               (28, 4, [1100, 1, 300, 0, 513, 77], 1200), (14, 2, [64, 3], 64),
+                                               (16, 8, [130, 129, 1], 256), (28, 4, [5000, 4097], 5100)])
+def test_decode_fused_quantization(dtype, Hq, Hkv, lens, Smax):
+    # an unsplit sequence is quantized by the attention kernel itself (one block with one KV head -- a
+    # tensor-parallel rank of 4 or 8 --, a thread-block cluster of the KV heads' blocks otherwise), a split
+    # one by the merge kernel; both must be the per-token quantizer's bits
     from llmqrt_b200.attention import attn_decode
     from oracle import quant as oq
-    B, Hkv, d = len(lens), 1, 128
+    B, d = len(lens), 128
     g = torch.Generator().manual_seed(Hq)
     q = torch.randn(B, Hq, d, generator=g).to(dtype).cuda()
     kc = torch.randn(B, Smax, Hkv, d, generator=g).to(dtype).cuda()

@@ -112,16 +112,43 @@ def test_int8_accumulators_bit_exact(ops, path, M, N, K):
 # Prefill-sized M: the four Qwen2-0.5B linears at M = 4096, and one Qwen2-7B shape at M = 16384 (the
 # token count of a 16 x 1024 prefill chunk, 128 x 256 tiles, persistent schedule).  The fp64 oracle is
 # evaluated on a few hundred sampled rows so that it stays a matter of seconds.
+# The shapes after the first five aim at the two-CTA (256 x 256 tile) kernel: a token count that is
+# no multiple of 256, an N that ends inside a tile, a ragged K, the smallest M that takes this kernel,
+# and an output whose row pitch is no multiple of 16 bytes (which must fall back to the one-CTA kernel).
 @pytest.mark.parametrize("M,N,K", [(4096, 896, 896), (4096, 128, 896), (4096, 4864, 896), (4096, 896, 4864),
-                                   (16384, 4608, 3584)])
+                                   (16384, 4608, 3584), (2300, 1000, 528), (1024, 4864, 896), (2048, 1001, 256),
+                                   (2049, 264, 3584)])
 def test_int8_accumulators_bit_exact_prefill_sizes(ops, M, N, K):
     from oracle import gemm as og
     g = torch.Generator().manual_seed(M + N * 3 + K)
     a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
     w = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
     acc = ops.int8_gemm_s32(a.cuda(), w.cuda()).cpu()
-    rows = torch.cat([torch.tensor([0, 127, 128, M - 1]), torch.randperm(M, generator=g)[:252]])
+    rows = torch.cat([torch.tensor([0, 127, 128, 255, 256, M - 129, M - 1]), torch.randperm(M, generator=g)[:249]])
     assert torch.equal(acc[rows], og.int8_accumulate(a[rows], w))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(2304, 1000, 896), (4096, 4608, 3584)])
+def test_int8_epilogues_prefill_sizes(ops, out_dtype, M, N, K):
+    # per-token x per-channel (bit-identical to the oracle's fp32 op order) and per-tensor epilogues of
+    # the kernel that serves M >= 1024, ragged edges included
+    from oracle import gemm as og
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    w = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
+    a_scale = torch.rand(M, generator=g) * 0.02 + 0.001
+    w_scale = torch.rand(N, generator=g) * 0.01 + 0.0005
+    bias = torch.randn(N, generator=g).to(out_dtype)
+    rows = torch.cat([torch.tensor([0, 127, 128, 255, 256, M - 1]), torch.randperm(M, generator=g)[:122]])
+    y = ops.int8_linear_per_channel(a.cuda(), w.cuda(), bias.cuda(), a_scale.cuda(), w_scale.cuda(), out_dtype)
+    y_ref = og.int8_linear_per_channel(a[rows], w, bias, a_scale[rows], w_scale, out_dtype)
+    assert bits_equal(y.cpu()[rows], y_ref)
+    if out_dtype == torch.float16:
+        yt = ops.int8_linear_per_tensor(a.cuda(), w.cuda(), bias.cuda(), 1e-4, 1.0)
+        yt_ref = og.int8_linear_per_tensor(a[rows], w, bias, 1e-4, 1.0)
+        frac, dist = ulp_mismatch_fraction(yt.cpu()[rows], yt_ref)
+        assert dist <= 1 and frac < 1e-3
 
 
 @pytest.mark.parametrize("path", list(PATHS))
@@ -282,7 +309,8 @@ def test_fp8_reference_unit_test_procedures(ops, path):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (100, 1536, 1536), (2048, 2048, 1536), (300, 136, 8960)])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (100, 1536, 1536), (2048, 2048, 1536), (300, 136, 8960),
+                                   (2100, 1160, 1000)])
 def test_gemm_16bit_tcgen05(ops, dtype, M, N, K):
     g = torch.Generator().manual_seed(M + N)
     a = torch.randn(M, K, generator=g).to(dtype)
