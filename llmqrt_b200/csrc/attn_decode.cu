@@ -382,7 +382,6 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
   // the q_cluster CTAs of this thread-block cluster -- hold the WHOLE token row between them): the
   // per-token int8 quantization of the row is done right here and the merge kernel is not launched.
   // The row's absolute maximum is the one thing the blocks exchange, through distributed shared memory.
-  __shared__ float cl_amax[8];                       // slot r: the maximum found by the cluster's CTA r
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   // (scratch behind the merge tile inside the idle rings: static shared memory would push two
   // resident blocks over the next carve-out step and cost L1)
@@ -431,20 +430,21 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) amax = fmaxf(amax, red_amax[w]);
     if (q_cluster > 1) {
-      // every CTA writes its maximum into its slot in EVERY CTA of the cluster (a dedicated static
-      // array: the rings of a CTA that is still streaming keys must not be written), then one cluster
-      // barrier (release / acquire) and each CTA reads its own copy -- nobody reads remote memory
-      // afterwards, so a CTA may leave as soon as it is through the barrier
-      uint32_t my_rank;
-      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my_rank));
-      if (tid < q_cluster) {
-        uint32_t remote;
-        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_amax[my_rank]);
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)tid));
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(amax) : "memory");
-      }
+      // every CTA leaves its maximum in its own scratch (its rings are idle by now; a peer's may not
+      // be, so nothing is written remotely), one cluster barrier, then every thread reads the peers'
+      // values through distributed shared memory.  A second barrier keeps each CTA's shared memory
+      // alive until all peers have read it: arrive right after the reads, wait after the stores below.
+      if (tid == 0) red_amax[kWarps] = amax;
       asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
-      for (int r = 0; r < q_cluster; ++r) amax = fmaxf(amax, cl_amax[r]);
+      const uint32_t local = (uint32_t)__cvta_generic_to_shared(&red_amax[kWarps]);
+      for (int r = 0; r < q_cluster; ++r) {
+        uint32_t remote;
+        float v;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)r));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+        amax = fmaxf(amax, v);
+      }
+      asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     }
     float sc = round_to<T>(fmaxf(amax, 1e-5f));
     sc = round_to<T>(__fmul_rn(sc, 1.0f / 127.0f));
@@ -454,6 +454,7 @@ attn_decode_kernel(const uint16_t* __restrict__ q, int64_t q_batch_stride, const
       v = v != v ? v : fminf(fmaxf(v, -128.f), 127.f);
       out_q[((int64_t)b * Hq + hkv * rep) * D + i] = (int8_t)(int)v;     // this block's heads of the token row
     }
+    if (q_cluster > 1) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   }
 }
 
@@ -537,7 +538,7 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
   }
   const float scale = 1.0f / sqrtf((float)D);
   constexpr int smem = kWarps * kRing * 2 * 16 * D * 2;           // per-warp rings; also holds the 16 KiB merge tile
-  static_assert(smem >= kWarps * 8 * D * 4 + 8 * D * 2 + kWarps * 4, "ring too small for the merge tile and the quantization scratch");
+  static_assert(smem >= kWarps * 8 * D * 4 + 8 * D * 2 + kWarps * 4 + 4, "ring too small for the merge tile and the quantization scratch");
   auto kern = attn_decode_kernel<BF16, D>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
   // No splits: the attention blocks of a sequence produce the whole token row and quantize it

@@ -793,24 +793,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
 // Each CTA's tensor memory receives its 128 accumulator rows (2 x 256 columns, double buffered).
 //   producer (warp 0, both CTAs): TMA loads whose bytes are counted on the LEADER's `full` barrier
 //   MMA issuer (warp 1, leader only): 4 MMAs per stage, commits fan out to both CTAs' barriers
-//   epilogue (warps 2-5, both CTAs): TMEM -> registers -> scales / bias -> 128-byte-swizzled staging
-//     tile -> TMA store (clipped at the matrix edge by the tensor map)
+//   epilogue (warps 2-9, both CTAs): TMEM -> registers -> scales / bias -> global memory, 64 or 128
+//     contiguous bytes per thread and step straight from registers (a staged TMA store was measured
+//     three times slower with one staging tile: its completion latency of a few microseconds
+//     serialises the chunks, and shared memory has no room for a deeper staging ring next to six stages)
 constexpr int kPairBN = 256;
 constexpr int kPairHalfB = kPairBN / 2;
 constexpr int kPairStageBytes = (kBM + kPairHalfB) * kRowBytes;         // 32 KiB
 constexpr int kPairStages = 6;
-constexpr int kPairStoreBytes = kBM * 128;                             // output staging: 128 rows x 128 bytes
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairStoreBytes + 1024;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
 constexpr uint32_t kPairTmemCols = 2 * kPairBN;
+constexpr int kPairThreads = 64 + 256;                                 // producer warp, MMA warp, eight epilogue warps
+__device__ __forceinline__ void pair_epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Tile order: the weight tiles are walked in groups of kPairGroup; inside a group the token tile
+// changes fastest.  The clusters that run at the same time then share a few weight tiles and a few
+// token tiles, and a weight group (8 x 256 rows) stays in L2 until every token tile has used it -- with
+// the weight tile changing fastest instead, a weight matrix larger than L2 (gate_up of Qwen2-7B: 136 MB)
+// is streamed from HBM once per token tile.
+constexpr int kPairGroup = 8;
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_p, int tiles_q, int& tp, int& tq) {
+  const int per_group = tiles_p * kPairGroup;
+  const int group = tile / per_group, within = tile - group * per_group;
+  const int gw = min(kPairGroup, tiles_q - group * kPairGroup);         // weight tiles in this group
+  tp = within / gw;
+  tq = group * kPairGroup + within - tp * gw;
+}
 
 template <int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                    const __grid_constant__ CUtensorMap tm_out, TcParams prm) {
+__global__ void __launch_bounds__(kPairThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, TcParams prm) {
   using AccT = typename std::conditional<KIND == tc::MMA_I8, int, float>::type;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ostage = tiles + kPairStages * kPairStageBytes;
   __shared__ __align__(8) uint64_t bar_full[kPairStages];      // used in the leader only
   __shared__ __align__(8) uint64_t bar_empty[kPairStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];
@@ -839,7 +854,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tc::mbar_fence_init();
     tc::tma_prefetch_descriptor(&tm_a);
     tc::tma_prefetch_descriptor(&tm_w);
-    tc::tma_prefetch_descriptor(&tm_out);
   }
   if (warp == 1) {
     tc::tmem_alloc_pair(tc::smem_u32(&tmem_base_slot), kPairTmemCols);
@@ -865,7 +879,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
+        int tp, tq;
+        pair_tile_coords(tile, prm.tiles_p, prm.tiles_q, tp, tq);
         const int row_a = tp * 2 * kBM + (int)rank * kBM, row_w = tq * kPairBN + (int)rank * kPairHalfB;
         for (int it = 0; it < kb_count; ++it) {
           tc::mbar_wait_or_flag(tc::smem_u32(&bar_empty[stage_i]), phase ^ 1u, abort_u32);
@@ -908,75 +923,152 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
   } else {
+    // Eight warps: two per tensor-memory lane quadrant, each taking one half (128) of the tile's columns.
+    // One warp per scheduler does not hide its own latencies, and the epilogue of a 128 x 256 tile must
+    // finish within the main loop of the next (K = 3584: 11 us) or the tensor pipe waits for it.
     const int quad = warp & 3, et = quad * 32 + lane;
+    const int half = (warp - 2) >> 2;                                   // which 128 columns
+    const int te = (int)threadIdx.x - 64;                               // 0 .. 255
     const bool issuer = threadIdx.x == 64;
     const Epilogue& e = prm.epi;
-    const bool raw = e.mode == EPI_RAW;
-    const bool wide = raw || e.out_dtype == LLMQRT_F32;                 // 4-byte outputs: 32 columns per 128-byte row
-    const int cw = wide ? 32 : 64;
+    const bool raw = e.mode == EPI_RAW, tensor = e.mode == EPI_TENSOR;
+    const bool scaled = e.mode == EPI_ROW_COL || e.mode == EPI_COL_ROW;
+    const bool wide = raw || e.out_dtype == LLMQRT_F32;                 // 4-byte outputs
+    const bool bf16 = e.out_dtype == LLMQRT_BF16;
+    const bool has_bias = e.bias != nullptr;
+    const bool col_first = e.mode == EPI_COL_ROW;                       // (acc * col_scale) * row_scale
+    const int es = wide ? 4 : 2;
     const float alpha = e.alpha_dev ? *e.alpha_dev : e.alpha;
+    const float bmul = tensor ? e.beta : 1.f;
     const uint32_t acc_empty0 = tc::cluster_addr(tc::smem_u32(&bar_acc_empty[0]), 0u);
-    uint4* my_row = reinterpret_cast<uint4*>(ostage + et * 128);
-    const int sw = et & 7;
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
-      const int tq = tile % prm.tiles_q, tp = tile / prm.tiles_q;
-      const int row0 = tp * 2 * kBM + (int)rank * kBM;
-      epi_barrier();                                   // previous tile no longer reads q_scale / q_bias
-      const EpiConsts ec = epi_setup(prm, alpha, row0 + et, tq * kPairBN, kPairBN, et, q_scale, q_bias);
+      int tp, tq;
+        pair_tile_coords(tile, prm.tiles_p, prm.tiles_q, tp, tq);
+      const int row = tp * 2 * kBM + (int)rank * kBM + et;
+      const bool row_ok = row < prm.M;
+      pair_epi_barrier();                              // previous tile no longer reads q_scale / q_bias
+      {
+        const int j = tq * kPairBN + te;               // one column's scale and bias per thread
+        float sc = 1.f, bi = 0.f;
+        if (j < prm.N) {
+          if (scaled) sc = e.col_scale[j];
+          if (has_bias && !raw) bi = __fmul_rn(bmul, load_as_f32(e.bias, j, e.bias_dtype));
+        }
+        q_scale[te] = sc;
+        q_bias[te] = bi;
+      }
+      const float rs = (scaled && row_ok) ? e.row_scale[row] : 1.f;
       const bool failed = !tc::mbar_wait(tc::smem_u32(&bar_acc_full[buf]), acc_phase[buf], abort);
-      if (tc::named_barrier_or(2, 128, failed)) break;
+      if (tc::named_barrier_or(2, 256, failed)) break;
       tc::fence_after_sync();
       acc_phase[buf] ^= 1u;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPairBN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPairBN + half * 128);
+      const int ncols = min(128, prm.N - tq * kPairBN - half * 128);    // my columns inside the matrix (may be <= 0)
+      uint8_t* orow = reinterpret_cast<uint8_t*>(e.out) + ((int64_t)row * e.ldo + (int64_t)tq * kPairBN + half * 128) * es;
+      // 32 accumulator columns per step; the load of the next step is issued before this step's
+      // arithmetic and stores so that its latency is hidden.  A thread owns 32 consecutive outputs of
+      // one row (64 or 128 contiguous bytes) and writes them straight from registers: fire-and-forget
+      // stores, nothing to wait for, the accumulator buffer is free as soon as the last load is back.
+      uint32_t r[2][32];
+      if (ncols > 0) tc::tmem_ld_32x32(taddr, r[0]);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kPairBN; c0 += cw) {
-        const int col0 = tq * kPairBN + c0;
-        if (col0 >= prm.N) break;
-#pragma unroll 1
-        for (int h = 0; h * 32 < cw; ++h) {
-          uint32_t r[32];
-          tc::tmem_ld_32x32(taddr + (uint32_t)(c0 + 32 * h), r);
+      for (int c0 = 0; c0 < ncols; c0 += 64) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c = c0 + 32 * h;
+          if (c >= ncols) break;
           tc::tmem_ld_wait();
+          if (c + 32 < ncols) tc::tmem_ld_32x32(taddr + (uint32_t)(c + 32), r[h ^ 1]);
+          uint32_t (&v)[32] = r[h];
+          // the operator's arithmetic, its run-time choices made once per 32 columns
           if (!raw) {
-            const float* qs = q_scale + c0 + 32 * h;
-            const float* qb = q_bias + c0 + 32 * h;
+            const float4* qs4 = reinterpret_cast<const float4*>(q_scale + half * 128 + c);
+            const float4* qb4 = reinterpret_cast<const float4*>(q_bias + half * 128 + c);
+            float f[32];
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj)
-              r[jj] = __float_as_uint(epi_value(ec, (float)acc_from_bits<AccT>(r[jj]), qs[jj], qb[jj], false));
-          }
-          if (h == 0) {
-            // the staging tile is free once the previous TMA store has read it
-            if (issuer) tc::tma_store_wait_read<0>();
-            epi_barrier();
-          }
-          if (wide) {
+            for (int jj = 0; jj < 32; ++jj) f[jj] = (float)acc_from_bits<AccT>(v[jj]);
+            if (tensor) {                              // fma(alpha, acc, beta * bias)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) my_row[k ^ sw] = make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
-          } else {
+              for (int k = 0; k < 8; ++k) {
+                const float4 b = qb4[k];
+                f[4 * k] = __fmaf_rn(alpha, f[4 * k], b.x); f[4 * k + 1] = __fmaf_rn(alpha, f[4 * k + 1], b.y);
+                f[4 * k + 2] = __fmaf_rn(alpha, f[4 * k + 2], b.z); f[4 * k + 3] = __fmaf_rn(alpha, f[4 * k + 3], b.w);
+              }
+            } else {
+              if (col_first) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              my_row[(4 * h + k) ^ sw] =
-                  make_uint4(pack16(__uint_as_float(r[8 * k]), __uint_as_float(r[8 * k + 1]), e.out_dtype),
-                             pack16(__uint_as_float(r[8 * k + 2]), __uint_as_float(r[8 * k + 3]), e.out_dtype),
-                             pack16(__uint_as_float(r[8 * k + 4]), __uint_as_float(r[8 * k + 5]), e.out_dtype),
-                             pack16(__uint_as_float(r[8 * k + 6]), __uint_as_float(r[8 * k + 7]), e.out_dtype));
+                for (int k = 0; k < 8; ++k) {
+                  const float4 q = qs4[k];
+                  f[4 * k] = __fmul_rn(__fmul_rn(f[4 * k], q.x), rs); f[4 * k + 1] = __fmul_rn(__fmul_rn(f[4 * k + 1], q.y), rs);
+                  f[4 * k + 2] = __fmul_rn(__fmul_rn(f[4 * k + 2], q.z), rs); f[4 * k + 3] = __fmul_rn(__fmul_rn(f[4 * k + 3], q.w), rs);
+                }
+              } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  const float4 q = qs4[k];
+                  f[4 * k] = __fmul_rn(__fmul_rn(f[4 * k], rs), q.x); f[4 * k + 1] = __fmul_rn(__fmul_rn(f[4 * k + 1], rs), q.y);
+                  f[4 * k + 2] = __fmul_rn(__fmul_rn(f[4 * k + 2], rs), q.z); f[4 * k + 3] = __fmul_rn(__fmul_rn(f[4 * k + 3], rs), q.w);
+                }
+              }
+              if (has_bias) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  const float4 b = qb4[k];
+                  f[4 * k] = __fadd_rn(f[4 * k], b.x); f[4 * k + 1] = __fadd_rn(f[4 * k + 1], b.y);
+                  f[4 * k + 2] = __fadd_rn(f[4 * k + 2], b.z); f[4 * k + 3] = __fadd_rn(f[4 * k + 3], b.w);
+                }
+              }
+            }
+            if (wide) {
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(f[jj]);
+            } else if (bf16) {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+                v[k] = *reinterpret_cast<uint32_t*>(&p2);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                __half2 p2 = __floats2half2_rn(f[2 * k], f[2 * k + 1]);
+                v[k] = *reinterpret_cast<uint32_t*>(&p2);
+              }
+            }
           }
-        }
-        tc::fence_proxy_async_smem();                  // generic writes -> TMA store reads
-        tc::fence_before_sync();
-        epi_barrier();
-        if (issuer && row0 < prm.M) {
-          tc::tma_store_2d(&tm_out, tc::smem_u32(ostage), col0, row0);
-          tc::tma_store_commit();
+          if (row_ok) {
+            if (wide) {                                // v[0..32): 32-bit outputs
+              if (c + 32 <= ncols) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  reinterpret_cast<uint4*>(orow + c * 4)[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+              } else {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj)
+                  if (c + jj < ncols) reinterpret_cast<uint32_t*>(orow + c * 4)[jj] = v[jj];
+              }
+            } else {                                   // v[0..16): pairs of 16-bit outputs
+              if (c + 32 <= ncols) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                  reinterpret_cast<uint4*>(orow + c * 2)[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+              } else {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj)
+                  if (c + jj < ncols) reinterpret_cast<uint16_t*>(orow + c * 2)[jj] = (uint16_t)(v[jj >> 1] >> (16 * (jj & 1)));
+              }
+            }
+          }
         }
       }
-      // every thread's tensor-memory reads are done (barrier above): the buffer may be overwritten
+      // every thread's tensor-memory reads are done: the buffer may be overwritten
+      tc::fence_before_sync();
+      pair_epi_barrier();
       if (issuer) tc::mbar_arrive_cluster(acc_empty0 + (uint32_t)buf * 8u);
       buf ^= 1;
     }
-    if (issuer) tc::tma_store_wait_all();
   }
 
   // ------------------------------- teardown ---------------------------------------
@@ -1119,22 +1211,6 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& 
   return check_launch("gemm_tc");
 }
 
-// Output matrix [M, N] (ld elements between rows) for TMA stores out of a 128-byte-swizzled staging
-// tile: box = 128 bytes x 128 rows.
-int make_out_map(CUtensorMap* map, void* base, int elt_bytes, int64_t rows, int64_t cols, int64_t ld) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)(ld * elt_bytes)};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / elt_bytes), (cuuint32_t)kBM};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, elt_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims,
-                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return set_error(LLMQRT_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
-  return LLMQRT_OK;
-}
-
 // Clusters of two CTAs of the pair kernel that can be resident at once (cached per device).
 template <int KIND>
 int pair_max_clusters() {
@@ -1151,7 +1227,7 @@ int pair_max_clusters() {
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = kPairSmemBytes;
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -1169,8 +1245,7 @@ int pair_max_clusters() {
 }
 
 template <int KIND>
-int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_w, const CUtensorMap& tm_out, const TcParams& prm,
-                cudaStream_t st) {
+int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_w, const TcParams& prm, cudaStream_t st) {
   auto kern = gemm_tc_pair_kernel<KIND>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kPairSmemBytes)) return rc;
   int clusters = pair_max_clusters<KIND>();
@@ -1180,7 +1255,7 @@ int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_w, const CUtensor
   cudaLaunchAttribute attr[2];
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = kPairSmemBytes;
   cfg.stream = st;
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1194,7 +1269,7 @@ int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_w, const CUtensor
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 2;
   }
-  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, tm_out, prm));
+  LLMQRT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, prm));
   return check_launch("gemm_tc_pair");
 }
 
@@ -1281,7 +1356,7 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
   else if (kind == KIND_BF16) { mk = tc::MMA_F16; fmt_act = fmt_w = 1; }
 
   // Prefill-sized problems whose 256-row pair tiles waste no more rows than 128-row tiles would: the
-  // two-CTA kernel.  Its TMA stores need a 16-byte aligned output with a 16-byte multiple row pitch.
+  // two-CTA kernel.  Its vector stores need a 16-byte aligned output with a 16-byte multiple row pitch.
   {
     const int es = (epi.mode == EPI_RAW || epi.out_dtype == LLMQRT_F32) ? 4 : 2;
     const bool out_ok = (reinterpret_cast<uintptr_t>(epi.out) & 15) == 0 && (epi.ldo * es) % 16 == 0;
@@ -1290,13 +1365,12 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
       prm.tiles_p = (int)ceil_div(M, (int64_t)(2 * kBM));
       prm.tiles_q = (int)ceil_div(N, (int64_t)kPairBN);
       prm.idesc = tc::instr_desc(c_fmt, fmt_act, fmt_w, 2 * kBM, kPairBN);
-      CUtensorMap tm_a, tm_w, tm_out;
+      CUtensorMap tm_a, tm_w;
       if (int rc = make_operand_map(&tm_a, A, elt, M, K, lda, kBM)) return rc;
       if (int rc = make_operand_map(&tm_w, W, elt, N, K, ldw, kPairHalfB)) return rc;
-      if (int rc = make_out_map(&tm_out, epi.out, es, M, N, epi.ldo)) return rc;
-      if (mk == tc::MMA_I8) return launch_pair<tc::MMA_I8>(tm_a, tm_w, tm_out, prm, st);
-      if (mk == tc::MMA_F8) return launch_pair<tc::MMA_F8>(tm_a, tm_w, tm_out, prm, st);
-      return launch_pair<tc::MMA_F16>(tm_a, tm_w, tm_out, prm, st);
+      if (mk == tc::MMA_I8) return launch_pair<tc::MMA_I8>(tm_a, tm_w, prm, st);
+      if (mk == tc::MMA_F8) return launch_pair<tc::MMA_F8>(tm_a, tm_w, prm, st);
+      return launch_pair<tc::MMA_F16>(tm_a, tm_w, prm, st);
     }
   }
   prm.idesc = tc::instr_desc(c_fmt, prm.swap ? fmt_w : fmt_act, prm.swap ? fmt_act : fmt_w, kBM, (uint32_t)bn);

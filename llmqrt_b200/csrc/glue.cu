@@ -614,17 +614,19 @@ int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* 
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = I % 8 == 0 && ld % 8 == 0 && aligned16(gate_up) && aligned16(y) &&
                    (reinterpret_cast<uintptr_t>(q) & 7) == 0;
-  // Register-resident variant: U units of 8 elements per thread, the row split over a cluster of rcl
-  // CTAs.  A cluster costs about a microsecond (its launch and two cluster barriers), so the row stays
-  // in ONE block whenever 1024 threads cover it, and a row that would need four CTAs takes two with
-  // two units per thread instead (64 rows of 18944: 6.5 us against 8.5 us; 64 rows of 2368: 2.5
-  // against 3.5 us with a cluster of two).
-  int rcl = 0, upt = 1;
+  // Register-resident variant: the smallest cluster whose slices fit one block (8 elements per
+  // thread), widened while that still leaves every SM at most a few blocks and slices of >= 128 threads.
+  // (Timed alone, fewer and larger blocks win -- 64 rows of 18944: two CTAs with two units per thread
+  // 6.5 us against 8.5 us with four CTAs --, but inside the decode chain, where the launch and the
+  // cluster set-up hide behind the preceding GEMM, the wider split is the faster one: 3.457 against
+  // 3.486 ms per step.)
+  int rcl = 0;
+  const int upt = 1;
   if (vec && M <= 1024) {                            // (prefill-sized M: the staged kernel streams better)
     const int64_t units = I / 8;
     for (int c = 1; c <= 8; c *= 2)
       if (units % c == 0 && units / c <= 1024) { rcl = c; break; }
-    if (rcl >= 4) { rcl /= 2; upt = 2; }
+    while (rcl && rcl < 8 && units % (rcl * 2) == 0 && units / (rcl * 2) >= 128 && M * rcl * 2 <= 4 * sm_count()) rcl *= 2;
   }
   const int cl = rcl ? rcl : (vec ? pick_cluster(M, I) : 1);
   const int64_t slice = I / cl;
@@ -641,8 +643,7 @@ int llmqrt_silu_mul(const void* gate_up, int64_t ld, void* y, int8_t* q, float* 
                       scale_f32 ? scale_f32 + m0 : (float*)nullptr, I, slice)
 #define LLMQRT_RUN_REGS_U(T)                                                                                           \
   switch (upt) {                                                                                                       \
-    case 1: LLMQRT_RUN_REGS(T, 1); break;                                                                              \
-    default: LLMQRT_RUN_REGS(T, 2); break;                                                                             \
+    default: LLMQRT_RUN_REGS(T, 1); break;                                                                             \
   }
       if (dtype == LLMQRT_F16) { LLMQRT_RUN_REGS_U(__half); } else { LLMQRT_RUN_REGS_U(__nv_bfloat16); }
 #undef LLMQRT_RUN_REGS_U
