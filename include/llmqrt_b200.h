@@ -313,10 +313,22 @@ int llmqrt_comm_allreduce(void* comm, const void* x, void* out, int dtype, int64
 /* llmqrt_rmsnorm with the residual arriving as tensor-parallel partial sums: residual =
  * all-reduce(partial) exactly as llmqrt_comm_allreduce computes it (rounded to the 16-bit type), then
  * h = x + residual, RMSNorm and the optional per-token int8 quantization, in one kernel
- * (H a multiple of 8, H <= 8192, M * H * 2 bytes within the communicator's capacity). */
+ * (H a multiple of 8, H <= 8192, M * H * 2 bytes within the communicator's capacity).  partial may be
+ * NULL when the partial sums have already been pushed by llmqrt_comm_int8_linear_per_channel. */
 int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x, void* x_out, const void* weight,
                                   float eps, void* y, int8_t* q, float* scale_f32, int dtype, int64_t M, int64_t H,
                                   llmqrt_stream_t stream);
+/* Row-parallel linear fused with the first half of that all-reduce: llmqrt_w8a8_int8_linear_per_channel
+ * whose 16-bit results do not go to an output tensor but, straight from the GEMM's epilogue, over
+ * NVLink into the peers' all-reduce buffers as this rank's contribution to the NEXT call.  That call
+ * must be llmqrt_comm_allreduce_rmsnorm with partial = NULL, the same M and H = N, which then only
+ * gathers, sums and normalises: GEMM + collective + normalisation in two kernels with no partial tensor
+ * in between.  16 < M <= 128, N a multiple of 8, N <= 8192.  (No counterpart in the reference, which has
+ * no tensor parallelism.) */
+int llmqrt_comm_int8_linear_per_channel(void* comm, const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw,
+                                        const void* bias, int bias_dtype, const float* a_scale, const float* w_scale,
+                                        int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace,
+                                        llmqrt_stream_t stream, int flags);
 int llmqrt_comm_set_poll_limit_ms(void* comm, int32_t ms);
 int llmqrt_comm_status(void* comm, int32_t* status_out);
 int llmqrt_comm_destroy(void* comm);

@@ -65,6 +65,7 @@ _PROTOS = {
     "llmqrt_comm_open_peer": (c_int, [P, I32, P]),
     "llmqrt_comm_allreduce": (c_int, [P, P, P, I32, I64, P]),
     "llmqrt_comm_allreduce_rmsnorm": (c_int, [P, P, P, P, P, F, P, P, P, I32, I64, I64, P]),
+    "llmqrt_comm_int8_linear_per_channel": (c_int, [P, P, I64, P, I64, P, I32, P, P, I32, I64, I64, I64, P, P, I32]),
     "llmqrt_comm_set_poll_limit_ms": (c_int, [P, c_int32]),
     "llmqrt_comm_status": (c_int, [P, ctypes.POINTER(ctypes.c_int32)]),
     "llmqrt_comm_destroy": (c_int, [P]),
@@ -86,7 +87,7 @@ def _bind(lib: ctypes.CDLL) -> list[str]:
     return missing
 
 
-ABI_VERSION = 4          # llmqrt_abi_version() of the sources these prototypes describe
+ABI_VERSION = 5          # llmqrt_abi_version() of the sources these prototypes describe
 
 _missing = _bind(_lib)
 if not _missing and _lib.llmqrt_abi_version() != ABI_VERSION:

@@ -77,7 +77,7 @@ extern "C" {
 
 const char* llmqrt_last_error(void) { return llmqrt::last_error_buffer(); }
 
-int llmqrt_abi_version(void) { return 4; }
+int llmqrt_abi_version(void) { return 5; }
 
 long long llmqrt_launch_count(void) { return llmqrt::launch_count(); }
 

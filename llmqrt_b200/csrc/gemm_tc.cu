@@ -32,6 +32,7 @@
 //
 // No multicast anywhere: every CTA fetches its own tiles with plain TMA loads.
 #include "gemm_w8a8.cuh"
+#include "peer_comm.cuh"
 #include "tc_primitives.cuh"
 
 #include <map>
@@ -66,6 +67,11 @@ struct TcParams {
   const uint32_t* awq_w;
   const uint32_t* awq_sz;
   int awq_kw, awq_kg, awq_g;       // K / 8, K / G, G
+  // Row-parallel output under tensor parallelism: instead of going to `out`, the 16-bit results are
+  // stored as the tagged words of the NEXT all-reduce call into the peers' buffers (peer_comm.cuh);
+  // the row kernel that consumes the sum then only gathers.
+  int comm_on, comm_threads, comm_two_step;
+  CommDev comm;
 };
 
 template <int BN> constexpr int stage_bytes() { return (kBM + BN) * kRowBytes; }
@@ -288,8 +294,32 @@ __device__ __forceinline__ void epi_stage_group8_any(const TcParams& prm, const 
 
 // Phase 2: staged block D[i0 .. i0+128, j0 .. j0+ncols) -> global memory, 16 bytes per thread and step.
 __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8_t* stage, int ncols, int i0, int j0,
-                                                int t) {
+                                                int t, unsigned comm_seq = 0u, bool comm_live = false) {
   const Epilogue& e = prm.epi;
+  if (prm.comm_on) {
+    // (swapped roles, 16-bit output, N a multiple of 8: checked on the host) a staged row is one token m
+    // with 128 channels; a 16-byte vector is unit u = n / 8 of the token's row and becomes two tagged words
+    if (!comm_live) return;                            // the communicator's status is raised: the consumer skips the sum
+    const CommDev& c = prm.comm;
+    const int rows_per_rank = (prm.M + c.world - 1) / c.world;
+#pragma unroll 1
+    for (int idx = t; idx < ncols * (kBM / 8); idx += 128) {
+      const int sr = idx / (kBM / 8), sv = idx - sr * (kBM / 8);
+      const int m = j0 + sr, n = i0 + sv * 8;
+      if (m >= prm.M || n >= prm.N) continue;
+      const uint4 val = *reinterpret_cast<const uint4*>(stage + sr * stage_pitch(true, 2) + sv * 16);
+      const long long w0 = comm_word0(m, n >> 3, prm.comm_threads);
+      if (prm.comm_two_step) {
+        const int owner = min(m / rows_per_rank, c.world - 1);
+        comm_push_one(c, comm_seq, owner, c.rank, w0, make_uint2(val.x, val.y));
+        comm_push_one(c, comm_seq, owner, c.rank, w0 + 32, make_uint2(val.z, val.w));
+      } else {
+        comm_push(c, comm_seq, w0, make_uint2(val.x, val.y));
+        comm_push(c, comm_seq, w0 + 32, make_uint2(val.z, val.w));
+      }
+    }
+    return;
+  }
   const int es = (e.mode == EPI_RAW || e.out_dtype == LLMQRT_F32) ? 4 : 2;
   const int per = 16 / es;                             // elements per 16-byte vector
   const int pitch = stage_pitch(prm.swap != 0, es);
@@ -348,6 +378,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int cluster_abort;                        // split mode: set in every CTA of the cluster by one that failed
+  __shared__ unsigned comm_seq_s;                      // push mode: the all-reduce call's sequence number ...
+  __shared__ int comm_live_s;                          // ... and whether the communicator is healthy
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort = &abort_flag;
@@ -387,6 +419,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   if (threadIdx.x != 0) {
     pdl_wait();
     pdl_trigger();
+  }
+  if (prm.comm_on && threadIdx.x == 64) {              // read by the epilogue warps after their first barrier
+    unsigned sq;
+    comm_live_s = comm_enter(prm.comm, &sq) ? 1 : 0;
+    comm_seq_s = sq;
   }
 
   // Work items: split mode -> exactly one tile per cluster (grid = tiles * S, non persistent);
@@ -661,7 +698,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           epi_stage_group8_any<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
         epi_barrier();
-        epi_drain_chunk(prm, stage, min(kChunk, prm.rows_q - j0), tp * kBM, j0, et);
+        epi_drain_chunk(prm, stage, min(kChunk, prm.rows_q - j0), tp * kBM, j0, et, comm_seq_s, comm_live_s != 0);
       }
       // accumulator buffer may be overwritten by the next-but-one tile
       tc::fence_before_sync();
@@ -764,7 +801,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           epi_stage_group8_any<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
         epi_barrier();
-        epi_drain_chunk(prm, stage, ncols, tp * kBM, j0, et);
+        epi_drain_chunk(prm, stage, ncols, tp * kBM, j0, et, comm_seq_s, comm_live_s != 0);
       }
     }
     // Nobody leaves while a peer may still be copying out of its `send` buffer (bounded: a peer that
@@ -1296,7 +1333,8 @@ bool pair_enabled() {
 }  // namespace
 
 int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
-            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w, const AwqOperand* awq) {
+            const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w, const AwqOperand* awq,
+            const CommPush* push) {
   const int elt = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
   if (awq) {                                           // W is produced in shared memory from the packed layer
     LLMQRT_REQUIRE(kind == KIND_F16 && awq->wq_t && awq->sz_t && awq->G > 0 && K % 32 == 0 && K % awq->G == 0 &&
@@ -1339,6 +1377,15 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
     // dequantizing warps only ever see 128-row weight tiles.
     prm.swap = 1;
     bn = 256;
+  }
+  if (push) {
+    LLMQRT_REQUIRE(prm.swap && !awq && epi.mode != EPI_RAW && epi.out_dtype != LLMQRT_F32 && N % 8 == 0 &&
+                   N / 8 <= push->threads,
+                   "tcgen05 gemm: output push needs the small-M schedule, a 16-bit output and N a multiple of 8");
+    prm.comm_on = 1;
+    prm.comm_threads = push->threads;
+    prm.comm_two_step = push->two_step;
+    prm.comm = push->dev;
   }
   prm.rows_p = prm.swap ? (int)N : (int)M;
   prm.rows_q = prm.swap ? (int)M : (int)N;

@@ -87,6 +87,35 @@ int llmqrt_w8a8_int8_linear_per_channel(const int8_t* a, int64_t lda, const int8
   return run(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream, flags);
 }
 
+int llmqrt_comm_int8_linear_per_channel(void* comm, const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw,
+                                        const void* bias, int bias_dtype, const float* a_scale, const float* w_scale,
+                                        int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace,
+                                        llmqrt_stream_t stream, int flags) {
+  LLMQRT_REQUIRE(comm != nullptr, "comm int8 linear: null communicator");
+  Comm* c = static_cast<Comm*>(comm);
+  if (int rc = check_common(a, lda, w, ldw, a, N, M, N, K)) return rc;       // (no output tensor: `a` stands in)
+  LLMQRT_REQUIRE(a_scale && w_scale, "comm int8 linear: null scale");
+  LLMQRT_REQUIRE(out_dtype == LLMQRT_F16 || out_dtype == LLMQRT_BF16, "comm int8 linear: dtype must be fp16/bf16");
+  LLMQRT_REQUIRE(!bias || bias_dtype == LLMQRT_F16 || bias_dtype == LLMQRT_BF16 || bias_dtype == LLMQRT_F32,
+                 "comm int8 linear: bad bias dtype");
+  LLMQRT_REQUIRE((flags & ~LLMQRT_GEMM_STATIC_WEIGHT) == 0, "comm int8 linear: unknown flags 0x%x", flags);
+  LLMQRT_REQUIRE(M > kStreamMaxM && M <= 128, "comm int8 linear: M = %lld is outside (16, 128], the range of the "
+                 "schedule whose epilogue pushes", (long long)M);
+  LLMQRT_REQUIRE(N % 8 == 0 && N <= 8192, "comm int8 linear: N must be a multiple of 8 and at most 8192");
+  CommPush push;
+  push.dev = c->dev;
+  push.threads = comm_row_threads(N);
+  push.two_step = comm_two_step(c->dev.world);
+  LLMQRT_REQUIRE(M * push.threads * 32 <= c->dev.slot_bytes, "comm int8 linear: M * N exceeds the communicator's capacity");
+  for (int p = 0; p < c->dev.world; ++p)
+    LLMQRT_REQUIRE(c->dev.base[p] != nullptr, "comm int8 linear: peer %d has not been opened", p);
+  Epilogue e{};
+  e.mode = EPI_COL_ROW; e.out_dtype = out_dtype; e.bias_dtype = bias_dtype; e.bias = bias; e.row_scale = a_scale;
+  e.col_scale = w_scale; e.out = nullptr; e.ldo = N;
+  return gemm_tc(KIND_I8, a, lda, w, ldw, M, N, K, e, workspace, (cudaStream_t)stream,
+                 (flags & LLMQRT_GEMM_STATIC_WEIGHT) != 0, nullptr, &push);
+}
+
 int llmqrt_w8a8_int8_gemm_s32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldo,
                               int64_t M, int64_t N, int64_t K, void* workspace, llmqrt_stream_t stream, int flags) {
   if (int rc = check_common(a, lda, w, ldw, acc, ldo, M, N, K)) return rc;

@@ -1,6 +1,7 @@
 // Internal interface between the W8A8 entry points and the two GEMM back ends.
 #pragma once
 #include "common.cuh"
+#include "peer_comm.cuh"
 
 namespace llmqrt {
 
@@ -28,7 +29,10 @@ struct AwqOperand {
 };
 int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
             const Epilogue& epi, void* workspace, cudaStream_t st, bool static_w = false,
-            const AwqOperand* awq = nullptr);
+            const AwqOperand* awq = nullptr, const CommPush* push = nullptr);
+// push != nullptr (decode-sized M only): the results do not go to epi.out but, as the tagged words of
+// the next all-reduce call, into the peers' buffers; llmqrt_comm_allreduce_rmsnorm with a null
+// `partial` completes the call.
 
 // Path selection shared by all entry points (0 auto, 1 streaming, 2 tcgen05).
 int gemm_path();

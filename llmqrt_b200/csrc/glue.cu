@@ -352,6 +352,8 @@ rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* 
 // `partial` to all ranks through the peer-mapped buffers, gathers the W copies, adds them in rank
 // order in fp32 and rounds to T -- exactly the stand-alone all-reduce -- and goes on with
 // h = x + that sum.  One kernel instead of all-reduce + RMSNorm.
+// partial == nullptr: the GEMM that produced the partial sums has already pushed them from its
+// epilogue (llmqrt_comm_int8_linear_per_channel), this kernel only gathers.
 // MAXT bounds the block size (512 leaves 128 registers per thread: the gathered copies of eight
 // ranks stay in registers).
 template <typename T, int MAXT>
@@ -369,8 +371,9 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
   // residual row and (thread 0) the call's sequence number travel to L2 at the same time.
   uint4 pv = make_uint4(0u, 0u, 0u, 0u);
   T e[8];
+  const bool pushed = partial == nullptr;
   if (on) {
-    pv = *reinterpret_cast<const uint4*>(partial + off + u * 8);
+    if (!pushed) pv = *reinterpret_cast<const uint4*>(partial + off + u * 8);
     load_unit<T, true>(x + off, u, e);
   }
   if (threadIdx.x == 0) {
@@ -389,15 +392,16 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
     if (live) {
       // Word placement (any bijection works, as every rank uses the same one): the two words of a
       // thread sit 32 words apart so that each store or poll of a warp covers 512 contiguous bytes.
-      const long long words[2] = {m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31),
-                                  m * (2 * (long long)blockDim.x) + (u >> 5) * 64 + (u & 31) + 32};
+      const long long words[2] = {comm_word0(m, u, (int)blockDim.x), comm_word0(m, u, (int)blockDim.x) + 32};
       // One step: every rank sends its row to every rank and all add the W copies themselves (W x the
       // payload leaves each rank).  Two steps, for many ranks: a row goes only to the rank that owns
       // it (rows are dealt out in equal runs), the owner adds the copies and sends the finished row,
       // rounded to T, to everyone (2 x the payload leaves each rank, one more hop of latency).
       const int rows_per_rank = ((int)gridDim.x + c.world - 1) / c.world;
       const int owner = two_step ? min((int)(m / rows_per_rank), c.world - 1) : c.rank;
-      if (two_step) {
+      if (pushed) {
+        // the GEMM's epilogue has sent this rank's rows (to everyone, or to their owners)
+      } else if (two_step) {
         comm_push_one(c, seq, owner, c.rank, words[0], make_uint2(pv.x, pv.y));
         comm_push_one(c, seq, owner, c.rank, words[1], make_uint2(pv.z, pv.w));
       } else {
@@ -518,6 +522,17 @@ inline bool aligned16(const void* p) { return p == nullptr || (reinterpret_cast<
 }  // namespace
 }  // namespace llmqrt
 
+namespace llmqrt {
+// two steps from 8 ranks on (or when LLMQRT_ALLREDUCE_TWO_STEP=1 asks for it, e.g. to test on fewer)
+int comm_two_step(int world) {
+  static const bool force_two_step = [] {
+    const char* v = getenv("LLMQRT_ALLREDUCE_TWO_STEP");
+    return v != nullptr && v[0] == '1';
+  }();
+  return (world >= 8 || force_two_step) ? 1 : 0;
+}
+}  // namespace llmqrt
+
 using namespace llmqrt;
 
 extern "C" {
@@ -578,19 +593,14 @@ int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x
   LLMQRT_REQUIRE(M >= 0 && M <= 0x7fffffffll && H > 0 && H % 8 == 0 && H <= 8192, "comm_allreduce_rmsnorm: need H %% 8 == 0 and H <= 8192");
   LLMQRT_REQUIRE(M * (((H / 8) + 31) / 32 * 32) * 32 <= c->dev.slot_bytes, "comm_allreduce_rmsnorm: M * H exceeds the communicator's capacity");
   if (M == 0) return LLMQRT_OK;
-  LLMQRT_REQUIRE(partial && x && weight && (y || q), "comm_allreduce_rmsnorm: null pointer");
+  LLMQRT_REQUIRE(x && weight && (y || q), "comm_allreduce_rmsnorm: null pointer");   // partial may be null: already pushed
   LLMQRT_REQUIRE(!q || scale_f32, "comm_allreduce_rmsnorm: quantized output needs scale_f32");
   LLMQRT_REQUIRE(aligned16(partial) && aligned16(x) && aligned16(x_out) && aligned16(weight) && aligned16(y) &&
                  (reinterpret_cast<uintptr_t>(q) & 7) == 0, "comm_allreduce_rmsnorm: pointers must be 16-byte aligned (q: 8)");
   for (int p = 0; p < c->dev.world; ++p)
     LLMQRT_REQUIRE(c->dev.base[p] != nullptr, "comm_allreduce_rmsnorm: peer %d has not been opened", p);
-  const unsigned threads = (unsigned)(((H / 8) + 31) / 32 * 32);
-  // two steps from 8 ranks on (or when LLMQRT_ALLREDUCE_TWO_STEP=1 asks for it, e.g. to test on fewer)
-  static const bool force_two_step = [] {
-    const char* v = getenv("LLMQRT_ALLREDUCE_TWO_STEP");
-    return v != nullptr && v[0] == '1';
-  }();
-  const int two_step = (c->dev.world >= 8 || force_two_step) ? 1 : 0;
+  const unsigned threads = (unsigned)comm_row_threads(H);
+  const int two_step = comm_two_step(c->dev.world);
   int rc;
 #define LLMQRT_RUN(T, MAXT)                                                                                        \
   rc = launch_chained(allreduce_rmsnorm_kernel<T, MAXT>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,            \

@@ -36,6 +36,23 @@ struct CommDev {                         // passed to kernels by value
   unsigned long long poll_limit_ns;      // bound of a poll
 };
 
+// What a row-parallel GEMM needs to deliver its output rows as the pushes of the next call (the row
+// kernel that consumes the sum then only gathers): the word of element 8u .. 8u+7 of row m depends on
+// the block size of that row kernel, and both must agree on one step or two.
+struct CommPush {
+  CommDev dev;
+  int threads;                           // block size of the consuming row kernel (comm_row_threads)
+  int two_step;
+};
+inline int comm_row_threads(int64_t H) { return (int)(((H / 8) + 31) / 32 * 32); }
+int comm_two_step(int world);            // glue.cu: two steps from 8 ranks on, or when the environment forces it
+// Word indices of unit u (elements 8u .. 8u+7) of row m: the two words of a unit sit 32 words apart so
+// that each store or poll of a warp covers 512 contiguous bytes.  (Any bijection works, as every
+// rank and both kernels use this one.)
+__host__ __device__ __forceinline__ long long comm_word0(long long m, long long u, int threads) {
+  return m * (2 * (long long)threads) + (u >> 5) * 64 + (u & 31);
+}
+
 struct Comm {                            // what the opaque handle of the C ABI points to
   CommDev dev;
   int device;

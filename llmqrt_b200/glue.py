@@ -13,13 +13,27 @@ def rmsnorm(x, weight, eps: float, residual=None, quantize: bool = False, want_y
     quantize: also return the per-token int8 quantization (q, scale_f32[M]) of y.
     comm: a tp.PeerAllreduce; `residual` then holds this rank's tensor-parallel PARTIAL sums and is
           all-reduced over the group first -- inside the same kernel when it fits the communicator,
-          else by NCCL (`residual` is then summed in place).
+          else by NCCL (`residual` is then summed in place).  `residual` may also be the token returned
+          by `comm.linear_push`: the GEMM has then sent the partial sums itself and this kernel only gathers.
     Returns (y or None, h or None, q or None, scale or None).
     """
-    dev = L.require_cuda(x, weight, residual)
+    from .tp import PushedPartial
+    pushed = isinstance(residual, PushedPartial)          # the partial sums are already on their way to the peers
+    dev = L.require_cuda(x, weight, None if pushed else residual)
     H = x.shape[-1]
     x2 = x.reshape(-1, H).contiguous()
     M = x2.shape[0]
+    if pushed:
+        if comm is None or (residual.M, residual.H) != (M, H):
+            raise RuntimeError("rmsnorm: pushed partial sums need their communicator and the same [M, H]")
+        h = torch.empty_like(x2)
+        y = torch.empty_like(x2) if want_y else None
+        q = torch.empty((M, H), dtype=torch.int8, device=dev) if quantize else None
+        s = torch.empty(M, dtype=torch.float32, device=dev) if quantize else None
+        with torch.cuda.device(dev):
+            L.call("llmqrt_comm_allreduce_rmsnorm", comm.handle, None, L.ptr(x2), L.ptr(h), L.ptr(weight),
+                   float(eps), L.ptr(y), L.ptr(q), L.ptr(s), L.dtype_code(x.dtype), M, H, L.stream(dev))
+        return (y.reshape(x.shape) if y is not None else None, h.reshape(x.shape), q, s)
     r2 = residual.reshape(-1, H).contiguous() if residual is not None else None
     if comm is not None and r2 is not None and r2.data_ptr() % 16:
         r2 = r2.clone()                                  # rank-local misalignment must not change the path

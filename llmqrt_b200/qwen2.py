@@ -178,14 +178,22 @@ class Qwen2Decoder:
                 glue.rope_kv_write(q, k, v, self.cos, self.sin, pos0=self.pos, pos_dev=None, k_cache=kc, v_cache=vc)
                 attn = attention.flash_attn_func(q, k, v, causal=True)
                 aq, _, a_s = ops.quantize_int8(attn.reshape(B * S, nq), per_token=True)
-            o = ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt, True)
+            M = B * S
+            push = decode and self.comm is not None and self.comm.push_ok(M, cfg.hidden)
+            if push:                                   # GEMM epilogue -> peers' buffers; the RMSNorm below gathers
+                o = self.comm.linear_push(aq, L_.wo, None, a_s, L_.so, dt, True)
+            else:
+                o = ops.int8_linear_per_channel(aq, L_.wo, None, a_s, L_.so, dt, True)
             if self.comm is None:
                 o = self._allreduce(o)
             _, h, yq, ys = glue.rmsnorm(h, L_.ln2, cfg.rms_eps, residual=o, quantize=True, want_y=False,
                                         comm=self.comm)
             gu = ops.int8_linear_per_channel(yq, L_.wgu, None, ys, L_.sgu, dt, True)                # [M, 2 I_local]
             _, mq, ms = glue.silu_mul(gu, quantize=True, want_y=False)
-            pending = ops.int8_linear_per_channel(mq, L_.wd, None, ms, L_.sd, dt, True)
+            if push:
+                pending = self.comm.linear_push(mq, L_.wd, None, ms, L_.sd, dt, True)
+            else:
+                pending = ops.int8_linear_per_channel(mq, L_.wd, None, ms, L_.sd, dt, True)
             if self.comm is None:
                 pending = self._allreduce(pending)
         return h, pending

@@ -8,6 +8,8 @@ of the partial outputs.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 
@@ -185,6 +187,13 @@ def greedy_select(val: torch.Tensor, idx: torch.Tensor, tp: int, group=None) -> 
     return both[..., 1].gather(0, best)[0].to(idx.dtype)
 
 
+class PushedPartial:
+    """Stands for partial sums that a GEMM has already sent to the peers (`PeerAllreduce.linear_push`)."""
+
+    def __init__(self, M: int, H: int, dtype):
+        self.M, self.H, self.dtype = M, H, dtype
+
+
 class PeerAllreduce:
     """Sum all-reduce of small 16-bit tensors over buffers that every rank of `group` maps from every
     other rank (one node, one process per GPU): llmqrt_comm_* of the C ABI.
@@ -230,6 +239,33 @@ class PeerAllreduce:
         four values, with the row's thread count rounded up to whole warps."""
         threads = (H // 8 + 31) // 32 * 32
         return H % 8 == 0 and H <= 8192 and M * threads * 32 <= 2 * ((self.max_bytes + 255) // 256 * 256)
+
+    def push_ok(self, M: int, H: int) -> bool:
+        """Whether a row-parallel int8 linear with M tokens and H outputs can send its results from the
+        GEMM's epilogue (`linear_push`): shapes only, so that every rank decides alike."""
+        if os.environ.get("LLMQRT_TP_PUSH", "1") == "0":           # A/B switch: the GEMM writes a tensor, the RMSNorm pushes
+            return False
+        return 16 < M <= 128 and self.fits_rows(M, H)
+
+    def linear_push(self, a, w, bias, a_scale, w_scale, out_dtype, static_weight: bool = False) -> "PushedPartial":
+        """int8 per-token x per-channel linear of a row-parallel layer whose 16-bit results go, from the
+        GEMM's epilogue, straight into the peers' all-reduce buffers.  The returned token must be handed
+        to `glue.rmsnorm(..., residual=token, comm=self)`, which gathers and sums (every rank alike)."""
+        L = self._L
+        M, K = a.shape
+        N = w.shape[0]
+        if not self.push_ok(M, N):
+            raise RuntimeError("linear_push: shape outside the pushing schedule (16 < M <= 128, M x N within capacity)")
+        a_s = a_scale.to(torch.float32).reshape(-1).contiguous()
+        w_s = w_scale.to(torch.float32).reshape(-1).contiguous()
+        if a_s.numel() != M or w_s.numel() != N:
+            raise RuntimeError("linear_push: a_scale must have M elements and w_scale N elements")
+        with torch.cuda.device(self.device):
+            L.call("llmqrt_comm_int8_linear_per_channel", self._comm, L.ptr(a), a.stride(0), L.ptr(w), w.stride(0),
+                   L.ptr(bias), L.dtype_code(bias.dtype) if bias is not None else L.F16, L.ptr(a_s), L.ptr(w_s),
+                   L.dtype_code(out_dtype), M, N, K, L.ptr(L.workspace(self.device)), L.stream(self.device),
+                   L.GEMM_STATIC_WEIGHT if static_weight else 0)
+        return PushedPartial(M, N, out_dtype)
 
     def allreduce(self, x: torch.Tensor) -> torch.Tensor:
         """In-place sum over the group.  A tensor that is not contiguous or not 16-byte aligned (a

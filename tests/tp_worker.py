@@ -50,6 +50,26 @@ def main():
             want = glue.rmsnorm(x, w, 1e-6, residual=comm.allreduce(part.clone()), quantize=True)
             got = glue.rmsnorm(x, w, 1e-6, residual=part.clone(), quantize=True, comm=comm)
             ok &= all(torch.equal(a, b) for a, b in zip(got, want))
+    # ---- row-parallel int8 linear that sends its partial sums from the GEMM's epilogue == the same linear
+    #      writing a tensor that the fused kernel then pushes (identical bits), three calls back to back ----
+    from llmqrt_b200 import ops
+    for dtype in (torch.float16, torch.bfloat16):
+        for M, N, K in ((64, 3584, 4736), (64, 3584, 256), (17, 1000, 512), (128, 256, 2048)):
+            g = torch.Generator().manual_seed(31 * M + N + K)
+            x = torch.randn(M, N, generator=g).to(dtype).to(dev)                       # same on every rank
+            wn = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype).to(dev)
+            gr = torch.Generator().manual_seed(9000 + rank)                            # this rank's shard
+            a = torch.randint(-128, 128, (M, K), generator=gr, dtype=torch.int8).to(dev)
+            w = torch.randint(-128, 128, (N, K), generator=gr, dtype=torch.int8).to(dev)
+            a_s = (torch.rand(M, generator=gr) * 1e-2 + 1e-3).to(dev)
+            w_s = (torch.rand(N, generator=gr) * 1e-2 + 1e-3).to(dev)
+            assert comm.push_ok(M, N)
+            for rep in range(3):
+                part = ops.int8_linear_per_channel(a, w, None, a_s, w_s, dtype)
+                want = glue.rmsnorm(x, wn, 1e-6, residual=part, quantize=True, comm=comm)
+                token = comm.linear_push(a, w, None, a_s, w_s, dtype)
+                got = glue.rmsnorm(x, wn, 1e-6, residual=token, quantize=True, comm=comm)
+                ok &= all(torch.equal(p, q) for p, q in zip(got, want))
     comm.check()
     if not ok:
         print(f"rank {rank}: peer all-reduce mismatch")
