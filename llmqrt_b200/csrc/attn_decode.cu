@@ -519,6 +519,10 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
     // Longer blocks than about a thousand keys stop paying: with ragged lengths the longest sequence
     // then runs alone at the end (32 sequences of 512..8192 keys: 59 us at 1024, 65 us at 4096).
     if (chunk > 1024 && max_seqlen > 2048) chunk = 1024;
+    // Two splits per sequence when the unsplit blocks alone would cover most of the SMs: not worth the
+    // merge kernel (batch 64 x 2 KV heads x 1150 keys: 16.0 us unsplit, 21.3 us as 2 x 1024 keys + merge;
+    // batch 64 x 1 KV head: 15.0 us unsplit against 14.3 us in three splits, left alone).
+    if (max_seqlen <= 2048 && ceil_div(max_seqlen, chunk) == 2 && (int64_t)B * Hkv * 4 >= 3 * (int64_t)sm_count()) chunk *= 2;
   }
   if (const char* env = getenv("LLMQRT_ATTN_CHUNK")) {                 // experiments: force the chunk
     const int v = atoi(env);
