@@ -293,10 +293,11 @@ __device__ __forceinline__ void epi_stage_group8_any(const TcParams& prm, const 
 }
 
 // Phase 2: staged block D[i0 .. i0+128, j0 .. j0+ncols) -> global memory, 16 bytes per thread and step.
+template <bool PUSH = false>
 __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8_t* stage, int ncols, int i0, int j0,
                                                 int t, unsigned comm_seq = 0u, bool comm_live = false) {
   const Epilogue& e = prm.epi;
-  if (prm.comm_on) {
+  if constexpr (PUSH) {
     // (swapped roles, 16-bit output, N a multiple of 8: checked on the host) a staged row is one token m
     // with 128 channels; a 16-byte vector is unit u = n / 8 of the token's row and becomes two tagged words
     if (!comm_live) return;                            // the communicator's status is raised: the consumer skips the sum
@@ -314,8 +315,11 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
         comm_push_one(c, comm_seq, owner, c.rank, w0, make_uint2(val.x, val.y));
         comm_push_one(c, comm_seq, owner, c.rank, w0 + 32, make_uint2(val.z, val.w));
       } else {
-        comm_push(c, comm_seq, w0, make_uint2(val.x, val.y));
-        comm_push(c, comm_seq, w0 + 32, make_uint2(val.z, val.w));
+#pragma unroll 1
+        for (int p = 0; p < c.world; ++p) {            // (rolled: this path must stay light on registers)
+          comm_push_one(c, comm_seq, p, c.rank, w0, make_uint2(val.x, val.y));
+          comm_push_one(c, comm_seq, p, c.rank, w0 + 32, make_uint2(val.z, val.w));
+        }
       }
     }
     return;
@@ -348,7 +352,11 @@ __device__ __forceinline__ void epi_drain_chunk(const TcParams& prm, const uint8
   }
 }
 
-template <int KIND, int BN, bool AWQ = false>
+// PUSH: the output rows go into the peers' all-reduce buffers (a kernel of its own: the pushing
+// epilogue needs 114 registers per thread against 67, and the register budget of a decode GEMM decides
+// whether its blocks can become resident, and fetch their first weights, beside the blocks of the
+// kernel before it -- with the push compiled into the common kernel the decode step lost 3.7 %).
+template <int KIND, int BN, bool AWQ = false, bool PUSH = false>
 __global__ void __launch_bounds__(AWQ ? kThreadsAwq : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_w, TcParams prm) {
@@ -420,10 +428,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     pdl_wait();
     pdl_trigger();
   }
-  if (prm.comm_on && threadIdx.x == 64) {              // read by the epilogue warps after their first barrier
-    unsigned sq;
-    comm_live_s = comm_enter(prm.comm, &sq) ? 1 : 0;
-    comm_seq_s = sq;
+  if constexpr (PUSH) {
+    if (threadIdx.x == 64) {                           // read by the epilogue warps after their first barrier
+      unsigned sq;
+      comm_live_s = comm_enter(prm.comm, &sq) ? 1 : 0;
+      comm_seq_s = sq;
+    }
   }
 
   // Work items: split mode -> exactly one tile per cluster (grid = tiles * S, non persistent);
@@ -698,7 +708,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           epi_stage_group8_any<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
         epi_barrier();
-        epi_drain_chunk(prm, stage, min(kChunk, prm.rows_q - j0), tp * kBM, j0, et, comm_seq_s, comm_live_s != 0);
+        epi_drain_chunk<PUSH>(prm, stage, min(kChunk, prm.rows_q - j0), tp * kBM, j0, et, PUSH ? comm_seq_s : 0u, PUSH && comm_live_s != 0);
       }
       // accumulator buffer may be overwritten by the next-but-one tile
       tc::fence_before_sync();
@@ -801,7 +811,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           epi_stage_group8_any<AccT>(prm, ec, r, q_scale + c0 + c, q_bias + c0 + c, c, et, stage);
         }
         epi_barrier();
-        epi_drain_chunk(prm, stage, ncols, tp * kBM, j0, et, comm_seq_s, comm_live_s != 0);
+        epi_drain_chunk<PUSH>(prm, stage, ncols, tp * kBM, j0, et, PUSH ? comm_seq_s : 0u, PUSH && comm_live_s != 0);
       }
     }
     // Nobody leaves while a peer may still be copying out of its `send` buffer (bounded: a peer that
@@ -1196,7 +1206,7 @@ cudaLaunchConfig_t make_config(int grid, int cluster, cudaStream_t st, cudaLaunc
 }
 
 // How many clusters of `cluster` CTAs of this kernel can be resident at once (cached per device).
-template <int KIND, int BN, bool AWQ = false>
+template <int KIND, int BN, bool AWQ = false, bool PUSH = false>
 int max_active_clusters(int cluster) {
   static std::mutex mu;
   static std::map<std::pair<int, int>, int> cache;
@@ -1205,7 +1215,7 @@ int max_active_clusters(int cluster) {
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find({dev, cluster});
   if (it != cache.end()) return it->second;
-  auto kern = gemm_tc_kernel<KIND, BN, AWQ>;
+  auto kern = gemm_tc_kernel<KIND, BN, AWQ, PUSH>;
   int n = 0;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes_of<BN, AWQ>()) == LLMQRT_OK) {
     cudaLaunchAttribute attr[2];
@@ -1219,9 +1229,9 @@ int max_active_clusters(int cluster) {
   return n;
 }
 
-template <int KIND, int BN, bool AWQ = false>
+template <int KIND, int BN, bool AWQ = false, bool PUSH = false>
 int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& tm_w, TcParams prm, cudaStream_t st) {
-  auto kern = gemm_tc_kernel<KIND, BN, AWQ>;
+  auto kern = gemm_tc_kernel<KIND, BN, AWQ, PUSH>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes_of<BN, AWQ>())) return rc;
   const int sms = sm_count();
   const int tiles = prm.tiles_p * prm.tiles_q;
@@ -1234,7 +1244,7 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& 
     float best = (float)ceil_div(tiles, sms) * ((float)prm.k_blocks + fixed);
     for (int s = 2; s <= 8; s *= 2) {
       if (prm.k_blocks < 2 * s || BN % s != 0 || BN / s < 8) continue;
-      const int active = max_active_clusters<KIND, BN, AWQ>(s);
+      const int active = max_active_clusters<KIND, BN, AWQ, PUSH>(s);
       if (active <= 0) continue;
       const float t = (float)ceil_div(tiles, active) * ((float)prm.k_blocks / s + fixed);
       if (t < best) { best = t; splits = s; }
@@ -1438,6 +1448,14 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
     CUtensorMap tm_w;
     if (int rc = make_packed_map(&tm_w, awq->wq_t, N, K / 8, kBM)) return rc;
     return launch_bn<tc::MMA_F16, true>(bn, tm_p, tm_q, tm_w, prm, st);
+  }
+  if (push) {                                          // (int8, weights as the 128-lane operand: checked above)
+    LLMQRT_REQUIRE(mk == tc::MMA_I8, "tcgen05 gemm: the output push is built for the int8 kind");
+    switch (bn) {
+      case 32: return launch<tc::MMA_I8, 32, false, true>(tm_p, tm_q, tm_p, prm, st);
+      case 64: return launch<tc::MMA_I8, 64, false, true>(tm_p, tm_q, tm_p, prm, st);
+      default: return launch<tc::MMA_I8, 128, false, true>(tm_p, tm_q, tm_p, prm, st);
+    }
   }
   if (mk == tc::MMA_I8) return launch_bn<tc::MMA_I8>(bn, tm_p, tm_q, tm_p, prm, st);
   if (mk == tc::MMA_F8) return launch_bn<tc::MMA_F8>(bn, tm_p, tm_q, tm_p, prm, st);
