@@ -355,8 +355,11 @@ rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* 
 // partial == nullptr: the GEMM that produced the partial sums has already pushed them from its
 // epilogue (llmqrt_comm_int8_linear_per_channel), this kernel only gathers.
 // MAXT bounds the block size (512 leaves 128 registers per thread: the gathered copies of eight
-// ranks stay in registers).
-template <typename T, int MAXT>
+// ranks stay in registers).  NS >= the number of ranks (2, 4 or 8) sizes the register array of the
+// gathered copies: with it fixed at 8 the kernel needed 122 registers per thread at any world size, and
+// a 448-thread block then fills the register file so that no block of the GEMM that follows (or
+// precedes) it in the decode chain can be resident on the same SM.
+template <typename T, int MAXT, int NS>
 __global__ void __launch_bounds__(MAXT)
 allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __restrict__ x, T* __restrict__ x_out,
                          const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
@@ -411,19 +414,24 @@ allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __re
       const unsigned long long t0 = comm_timer_ns();
       bool ok = true;
       if (owner == c.rank) {
-        uint4 d[kCommMaxWorld][2];
-        ok = comm_gather_all<kCommMaxWorld, 2>(c, seq, 0, c.world, words, t0, d);
-        if (ok) {
+        // at most four sources per round of polls: eight at once need 64 registers for the copies alone
+        constexpr int NB = NS > 4 ? 4 : NS;
+#pragma unroll 1
+        for (int s0 = 0; s0 < c.world && ok; s0 += NB) {
+          uint4 d[NB][2];
+          ok = comm_gather_all<NB, 2>(c, seq, s0, min(NB, c.world - s0), words, t0, d);
+          if (ok) {
 #pragma unroll
-          for (int s = 0; s < kCommMaxWorld; ++s) {    // rank order: the same bits on every rank
-            if (s < c.world) {
-              const uint2 p0 = make_uint2(d[s][0].x, d[s][0].z), p1 = make_uint2(d[s][1].x, d[s][1].z);
-              const T* e0 = reinterpret_cast<const T*>(&p0);
-              const T* e1 = reinterpret_cast<const T*>(&p1);
+            for (int s = 0; s < NB; ++s) {             // rank order: the same bits on every rank
+              if (s0 + s < c.world) {
+                const uint2 p0 = make_uint2(d[s][0].x, d[s][0].z), p1 = make_uint2(d[s][1].x, d[s][1].z);
+                const T* e0 = reinterpret_cast<const T*>(&p0);
+                const T* e1 = reinterpret_cast<const T*>(&p1);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                acc[j] += to_f32<T>(e0[j]);
-                acc[4 + j] += to_f32<T>(e1[j]);
+                for (int j = 0; j < 4; ++j) {
+                  acc[j] += to_f32<T>(e0[j]);
+                  acc[4 + j] += to_f32<T>(e1[j]);
+                }
               }
             }
           }
@@ -602,14 +610,21 @@ int llmqrt_comm_allreduce_rmsnorm(void* comm, const void* partial, const void* x
   const unsigned threads = (unsigned)comm_row_threads(H);
   const int two_step = comm_two_step(c->dev.world);
   int rc;
-#define LLMQRT_RUN(T, MAXT)                                                                                        \
-  rc = launch_chained(allreduce_rmsnorm_kernel<T, MAXT>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,            \
+#define LLMQRT_RUN_NS(T, MAXT, NS)                                                                                 \
+  rc = launch_chained(allreduce_rmsnorm_kernel<T, MAXT, NS>, dim3((unsigned)M, 1, 1), dim3(threads, 1, 1), 0,        \
                       (cudaStream_t)stream, 1, c->dev, reinterpret_cast<const T*>(partial),                          \
                       reinterpret_cast<const T*>(x), reinterpret_cast<T*>(x_out), reinterpret_cast<const T*>(weight), \
                       eps, reinterpret_cast<T*>(y), q, scale_f32, H, two_step)
+#define LLMQRT_RUN(T, MAXT)                                       \
+  do {                                                            \
+    if (c->dev.world <= 2) LLMQRT_RUN_NS(T, MAXT, 2);             \
+    else if (c->dev.world <= 4) LLMQRT_RUN_NS(T, MAXT, 4);        \
+    else LLMQRT_RUN_NS(T, MAXT, 8);                               \
+  } while (0)
   if (threads <= 512) { if (dtype == LLMQRT_F16) LLMQRT_RUN(__half, 512); else LLMQRT_RUN(__nv_bfloat16, 512); }
   else { if (dtype == LLMQRT_F16) LLMQRT_RUN(__half, 1024); else LLMQRT_RUN(__nv_bfloat16, 1024); }
 #undef LLMQRT_RUN
+#undef LLMQRT_RUN_NS
   if (rc) return rc;
   return check_launch("allreduce_rmsnorm");
 }
