@@ -470,7 +470,7 @@ attn_decode_combine_kernel(const int32_t* __restrict__ seqlens, uint16_t* __rest
                            int8_t* __restrict__ out_q, float* __restrict__ out_scale) {
   extern __shared__ __align__(16) uint8_t row_raw[];
   __shared__ float red[32];
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   const int b = blockIdx.x;
   const int L = min(seqlens[b], max_len);          // same clamp as the main kernel
   const int n_splits = (L + chunk - 1) / chunk;

@@ -61,11 +61,12 @@ int ensure_dynamic_smem(const void* func, int bytes);
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-// Entry of a kernel whose successor is typically a GEMM: the successor may start (and request its
-// weights, which nobody in the chain writes) while this kernel is still waiting for its own
-// predecessor.  Safe because every chained kernel waits before it reads or writes anything else, and
-// a wait only returns after the predecessor, hence the predecessor's predecessor, has completed.
-__device__ __forceinline__ void pdl_trigger_then_wait() {
+// Entry of a small kernel whose successor is typically a GEMM: it waits for its own predecessor first
+// and releases its dependents right after, so the successor's blocks become resident -- and request
+// their weights, which nobody in the chain writes -- while this kernel does its work.  (Releasing
+// BEFORE the wait lets the successor start while the predecessor GEMM is still streaming; its early
+// weight requests then compete with that GEMM's for HBM, and the step was measured slower.)
+__device__ __forceinline__ void pdl_wait_then_trigger() {
   pdl_wait();
   pdl_trigger();
 }

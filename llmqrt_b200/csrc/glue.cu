@@ -109,7 +109,7 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __res
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_ss, slot_amax;
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -162,7 +162,7 @@ silu_mul_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, in
   constexpr int U = VEC ? 8 : 1;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float slot_amax;
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   T* row = reinterpret_cast<T*>(smem);
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(1024)
 silu_mul_regs_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, int8_t* __restrict__ q,
                      float* __restrict__ scale_f32, int64_t I, int64_t slice) {
   __shared__ float slot_amax;
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
   float f[U][8];
@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(1024)
 rmsnorm_regs_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ x_out,
                     const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
                     float* __restrict__ scale_f32, int64_t H) {
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   const int64_t m = blockIdx.x, u = threadIdx.x;
   const bool on = u * 8 < H;
   const int64_t off = m * H;
@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(MAXT)
 allreduce_rmsnorm_kernel(CommDev c, const T* __restrict__ partial, const T* __restrict__ x, T* __restrict__ x_out,
                          const T* __restrict__ weight, float eps, T* __restrict__ y, int8_t* __restrict__ q,
                          float* __restrict__ scale_f32, int64_t H, int two_step) {
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   __shared__ unsigned s_seq;
   __shared__ int s_ok;
   const int64_t m = blockIdx.x, u = threadIdx.x;

@@ -98,7 +98,7 @@ template <typename T, bool FP8>
 __global__ void __launch_bounds__(kThreads)
 quantize_per_token_kernel(const T* __restrict__ x, int64_t K, int64_t ldx, uint8_t* __restrict__ q,
                           T* __restrict__ scale_x, float* __restrict__ scale_f32, float scale_mul, bool vec_ok) {
-  pdl_trigger_then_wait();
+  pdl_wait_then_trigger();
   const int64_t m = blockIdx.x;
   const T* row = x + m * ldx;
   float amax = block_max(row_absmax<T>(row, K, vec_ok));

@@ -227,7 +227,9 @@ def test_decode_append_on_a_full_cache_writes_nothing():
 @pytest.mark.parametrize("Hq,Hkv,lens,Smax", [(4, 1, [1100, 1, 300, 0, 513], 1200), (3, 1, [40, 7, 64], 64),
                                                (7, 1, [200, 199], 256), (4, 1, [5000, 4097], 5100),
                                                (28, 4, [1100, 1, 300, 0, 513, 77], 1200), (14, 2, [64, 3], 64),
-                                               (16, 8, [130, 129, 1], 256), (28, 4, [5000, 4097], 5100)])
+                                               (16, 8, [130, 129, 1], 256), (28, 4, [5000, 4097], 5100),
+                                               # enough sequences that two splits give way to one block per KV head
+                                               (14, 2, [1100] * 60 + [1, 0, 513, 77], 1200)])
 def test_decode_fused_quantization(dtype, Hq, Hkv, lens, Smax):
     # an unsplit sequence is quantized by the attention kernel itself (one block with one KV head -- a
     # tensor-parallel rank of 4 or 8 --, a thread-block cluster of the KV heads' blocks otherwise), a split
