@@ -10,9 +10,9 @@
 // the kernel is a pure weight streamer.
 //
 // Split-K for skinny problems: when there are fewer tiles than SMs, the reduction dimension of a tile
-// is divided among the 2, 4 or 8 CTAs of a thread-block CLUSTER.  Each CTA accumulates its K range in
+// is divided among the 2 to 8 CTAs of a thread-block CLUSTER.  Each CTA accumulates its K range in
 // tensor memory, then the cluster reduce-scatters through distributed shared memory: CTA r owns
-// BN/S accumulator columns, every CTA bulk-copies its slice of those columns into r's shared memory
+// about BN/S accumulator columns (whole groups of eight), every CTA bulk-copies its slice of those columns into r's shared memory
 // after one cluster barrier, r adds the S contributions in rank order (deterministic) and runs the
 // epilogue; peers are released by remote mbarrier arrivals instead of a second cluster barrier.  No
 // global scratch, no atomics, no second kernel.
@@ -54,7 +54,7 @@ constexpr int kEpiStageBytes = 18 * 1024;  // staging tile for one chunk (worst 
 struct TcParams {
   int rows_p, rows_q;              // extents of P and Q (M/N or N/M)
   int k_blocks;                    // ceil(K bytes / 128)
-  int tiles_p, tiles_q, splits;    // splits == cluster size along K (1, 2, 4 or 8)
+  int tiles_p, tiles_q, splits;    // splits == cluster size along K (1 .. 8)
   int swap;                        // 0: P = tokens (i -> m, j -> n); 1: P = weights (i -> n, j -> m)
   int early_w;                     // weight tiles of the first ring may be requested before the dependency wait
   int M, N;
@@ -146,6 +146,9 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_local, uint32_t 
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Split mode: the BN accumulator columns are dealt out to the S CTAs of the cluster in groups of eight,
+// as evenly as S allows (S need not divide BN / 8: a cluster of three owns 24 + 24 + 16 of 64 columns).
+__device__ __forceinline__ int split_col_begin(int owner, int bn, int S) { return (owner * (bn / 8) / S) * 8; }
 
 // ---- epilogue --------------------------------------------------------------------------------------
 // Arithmetic of one output element.  `var` is the scale that changes with the accumulator column
@@ -366,7 +369,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   constexpr int kStageBytes = stage_bytes<BN>();
   constexpr int kPkBytes = kPackedBytes;
   constexpr uint32_t kTmemCols = tmem_cols<BN>();
-  constexpr int kBurst = kStages >= 8 ? 4 : (kStages >= 4 ? 2 : 1);  static_assert(BN > 128 || kStages * kStageBytes >= 2 * kBM * BN * 4, "ring too small for the reduce buffers");
+  constexpr int kBurst = kStages >= 8 ? 4 : (kStages >= 4 ? 2 : 1);  static_assert(BN > 128 || kStages * kStageBytes >= (2 * BN + 64) * kBM * 4, "ring too small for the reduce buffers");
   static_assert(kStages >= 3, "pipeline too shallow");
 
   extern __shared__ uint8_t smem_raw[];
@@ -684,8 +687,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         ec = epi_setup(prm, alpha, tp * kBM + et, tq * BN, BN, et, q_scale, q_bias);
       } else {
         // split mode: the scales of the columns this CTA owns, fetched while the MMAs still run
-        const int cpo = BN / S;
-        ec_split = epi_setup(prm, alpha, tp * kBM + et, tq * BN + my_split * cpo, cpo, et, q_scale, q_bias);
+        const int col0 = split_col_begin(my_split, BN, S), cpo = split_col_begin(my_split + 1, BN, S) - col0;
+        ec_split = epi_setup(prm, alpha, tp * kBM + et, tq * BN + col0, cpo, et, q_scale, q_bias);
       }
       // The four epilogue warps must agree on leaving the loop: OR the failure over all 128 threads.
       const bool failed = !tc::mbar_wait(tc::smem_u32(&bar_acc_full[buf]), acc_phase[buf], abort);
@@ -721,14 +724,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   if constexpr (BN <= 128) {
   if (S > 1) {
     // The pipeline ring is dead once a CTA's MMAs have retired.  It is reused as
-    //   recv = ring[0, BN*512)          [source rank][owned column][128 rows] 32-bit words
-    //   send = ring[BN*512, BN*1024)    [accumulator column][128 rows]
+    //   recv = ring[0, S * cpo_max * 512)   [source rank][owned column][128 rows] 32-bit words
+    //   send = behind it, BN * 512 bytes    [accumulator column][128 rows]
     // Each CTA parks its accumulator in `send`, and after a cluster barrier (every ring dead) one
     // thread pushes slice o of `send` into `recv` of CTA o with a bulk shared->shared copy that
     // completes on o's `bar_reduce`.
-    const int cpo = BN / S;                            // accumulator columns owned by each CTA
-    const uint32_t slice_bytes = (uint32_t)cpo * kBM * 4;
-    uint32_t* send = reinterpret_cast<uint32_t*>(tiles + BN * kBM * 4);
+    const int col0 = split_col_begin(my_split, BN, S);                 // accumulator columns owned by this CTA:
+    const int cpo = split_col_begin(my_split + 1, BN, S) - col0;        // [col0, col0 + cpo)
+    const uint32_t slice_bytes = (uint32_t)cpo * kBM * 4;              // what every CTA sends to this one
+    const int cpo_max = ((BN / 8 + S - 1) / S) * 8;
+    uint32_t* send = reinterpret_cast<uint32_t*>(tiles + S * cpo_max * kBM * 4);
     const bool own_healthy = abort_flag == 0;          // own MMAs finished (epilogue warps waited for them)
     const int quad = warp & 3, et = quad * 32 + lane;
     const bool epi_warp = warp >= 2 && warp < 6;       // (AWQ mode has more warps behind them)
@@ -768,10 +773,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     const bool healthy = own_healthy && *reinterpret_cast<volatile int*>(&cluster_abort) == 0;
     if (!healthy && threadIdx.x == 64) abort_flag = 1;                 // reported through the status word at exit
     if (threadIdx.x == 64 && healthy) {
-      for (int o = 0; o < S; ++o)
-        bulk_copy_to_cta(tc::smem_u32(tiles) + (uint32_t)my_split * slice_bytes,
-                         tc::smem_u32(send) + (uint32_t)o * slice_bytes, slice_bytes, tc::smem_u32(&bar_reduce),
-                         (uint32_t)o);
+      for (int o = 0; o < S; ++o) {                   // owner o receives its columns of my accumulator
+        const int ob = split_col_begin(o, BN, S);
+        const uint32_t obytes = (uint32_t)(split_col_begin(o + 1, BN, S) - ob) * kBM * 4;
+        bulk_copy_to_cta(tc::smem_u32(tiles) + (uint32_t)my_split * obytes, tc::smem_u32(send) + (uint32_t)ob * kBM * 4,
+                         obytes, tc::smem_u32(&bar_reduce), (uint32_t)o);
+      }
     }
     // Once every slice addressed to this CTA has landed, the peers' `send` buffers are no longer
     // being read on its behalf: tell each of them.  A CTA leaves once all S owners have said so, which
@@ -790,7 +797,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       const AccT* rbuf = reinterpret_cast<const AccT*>(tiles);
 #pragma unroll 1
       for (int c0 = 0; c0 < cpo; c0 += kChunk) {
-        const int j0 = tq * BN + my_split * cpo + c0;
+        const int j0 = tq * BN + col0 + c0;
         if (j0 >= prm.rows_q) break;
         const int ncols = min(min(kChunk, cpo - c0), prm.rows_q - j0);
         epi_barrier();
@@ -1242,8 +1249,8 @@ int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, const CUtensorMap& 
     // reduce-scatter and epilogue).
     const float fixed = 8.f;
     float best = (float)ceil_div(tiles, sms) * ((float)prm.k_blocks + fixed);
-    for (int s = 2; s <= 8; s *= 2) {
-      if (prm.k_blocks < 2 * s || BN % s != 0 || BN / s < 8) continue;
+    for (int s = 2; s <= 8; ++s) {                     // (any size: 36 tiles fit as clusters of three, not of four)
+      if (prm.k_blocks < 2 * s || BN / 8 < s) continue;
       const int active = max_active_clusters<KIND, BN, AWQ, PUSH>(s);
       if (active <= 0) continue;
       const float t = (float)ceil_div(tiles, active) * ((float)prm.k_blocks / s + fixed);

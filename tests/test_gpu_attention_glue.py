@@ -228,6 +228,7 @@ def test_decode_append_on_a_full_cache_writes_nothing():
                                                (7, 1, [200, 199], 256), (4, 1, [5000, 4097], 5100),
                                                (28, 4, [1100, 1, 300, 0, 513, 77], 1200), (14, 2, [64, 3], 64),
                                                (16, 8, [130, 129, 1], 256), (28, 4, [5000, 4097], 5100),
+                                               (6, 3, [70, 33, 128], 128), (14, 7, [200], 256),      # clusters of 3 and 7 blocks
                                                # enough sequences that two splits give way to one block per KV head
                                                (14, 2, [1100] * 60 + [1, 0, 513, 77], 1200)])
 def test_decode_fused_quantization(dtype, Hq, Hkv, lens, Smax):

@@ -21,4 +21,4 @@ def test_tensor_parallel_decoder_matches_oracle(world, two_step):
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + 2 * world + int(two_step)),
            os.path.join(ROOT, "tests", "tp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
-    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-9000:]

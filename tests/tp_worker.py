@@ -95,7 +95,10 @@ def main():
     dist.barrier()
 
     from llmqrt_b200.qwen2 import Qwen2Config, Qwen2Decoder
-    cfg = Qwen2Config.tiny()
+    # 4 query / 2 KV heads divide among up to 4 ranks; 8 ranks get 12 query / 4 KV heads: every KV head on
+    # two ranks, its three query heads split 2 + 1 (the uneven case of Qwen2-7B's 28 / 4 heads on 8 ranks)
+    cfg = Qwen2Config.tiny() if world <= 4 else Qwen2Config(num_layers=2, hidden=256, intermediate=512, num_heads=12,
+                                                            num_kv_heads=4, head_dim=64, vocab=1024)
     B, S, steps, max_len = 3, 21, 3, 48
     model = Qwen2Decoder(cfg, dev, batch=B, max_seq_len=max_len, tp=world, rank=rank, group=dist.group.WORLD, seed=5)
     prompt = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(0))
