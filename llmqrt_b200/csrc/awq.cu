@@ -357,8 +357,30 @@ int llmqrt_awq_gemm(const void* x, int64_t ldx, const uint32_t* wq_t, const uint
   e.ldo = ldo;
   const __half* xp = reinterpret_cast<const __half*>(x);
   cudaStream_t st = (cudaStream_t)stream;
+  if (M >= 1024 && workspace && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ldo % 8 == 0) {
+    // A thousand tokens and more: the GEMM is compute-bound, the two-CTA fp16 kernel runs about twice
+    // as fast as the kernel that dequantizes into its own shared memory (whose dequantizing warps and
+    // tensor core share the SM's shared-memory bandwidth), and writing the fp16 weights out once and
+    // reading them back costs a tenth of the GEMM.  The weights are expanded panel by panel into the
+    // workspace (same rounding: fp16((v - z) * s)) and each panel is multiplied by the dense kernel.
+    const int64_t cap_rows = (int64_t)(LLMQRT_WS_PARTIAL_BYTES / (size_t)(K * 2)) / 256 * 256;
+    if (cap_rows >= 256) {
+      __half* deq = reinterpret_cast<__half*>(ws_partials(workspace));
+      for (int64_t n0 = 0; n0 < N; n0 += cap_rows) {
+        const int64_t nc = (N - n0 < cap_rows) ? (N - n0) : cap_rows;
+        awq_dequantize_t_kernel<<<(unsigned)ceil_div(nc * (K / 8), 256), 256, 0, st>>>(
+            wq_t + n0 * (K / 8), sz_t + n0 * (K / group_size), K / 8, nc, group_size, deq);
+        if (int rc = check_launch("awq_dequantize_t")) return rc;
+        Epilogue ep = e;
+        ep.out = reinterpret_cast<__half*>(out) + n0;
+        ep.bias = bias ? reinterpret_cast<const __half*>(bias) + n0 : nullptr;
+        if (int rc = gemm_tc(KIND_F16, x, ldx, deq, K, M, nc, K, ep, workspace, st)) return rc;
+      }
+      return LLMQRT_OK;
+    }
+  }
   if (M > 64) {
-    // Prefill-sized M: still ONE kernel.  The tcgen05 GEMM runs with four extra warps that turn the
+    // 64 < M < 1024: ONE kernel.  The tcgen05 GEMM runs with four extra warps that turn the
     // packed 4-bit tiles into fp16 operand tiles in shared memory (same rounding: fp16((v - z) * s)),
     // so the dequantized weights never exist in global memory.
     e.out = out;

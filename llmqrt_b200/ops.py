@@ -209,8 +209,9 @@ def awq_dequantize_t(packed: AwqPacked) -> torch.Tensor:
 
 
 def awq_gemm(x: torch.Tensor, packed: AwqPacked, bias=None) -> torch.Tensor:
-    """C[M, N] fp16 = x[M, K] fp16 @ dequant(W) (+ bias): one fused kernel at every M (a weight-streaming
-    mma.sync kernel up to 64 tokens, the tcgen05 GEMM with in-kernel dequantization above)."""
+    """C[M, N] fp16 = x[M, K] fp16 @ dequant(W) (+ bias): one fused kernel below 1024 tokens (a weight-streaming
+    mma.sync kernel up to 64, the tcgen05 GEMM with in-kernel dequantization above); from 1024 tokens on the
+    weights are expanded panel-wise into the workspace and multiplied by the two-CTA fp16 kernel."""
     dev = L.require_cuda(x, packed.wq_t, bias)
     x2 = _rows(x)
     M, K = x2.shape

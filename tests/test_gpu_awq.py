@@ -59,6 +59,24 @@ def test_gemm_sweep(ops, M, N, K):
     assert rel_fro(y, ref.to(torch.float16)) < 1e-2
 
 
+def test_gemm_many_tokens_weight_panels(ops):
+    # from 1024 tokens on the weights are expanded panel by panel into the workspace and multiplied by the dense
+    # fp16 kernel: a layer whose fp16 form (9600 x 8960 x 2 B = 172 MB) exceeds one 160 MB panel takes two
+    from oracle import awq as oa
+    K, N, G, M = 8960, 9600, 128, 1024
+    qw, qz, sc = oa.random_layer(K, N, G, seed=11)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(torch.float16)
+    bias = torch.randn(N, generator=g).to(torch.float16)
+    packed = ops.AwqPacked(qw.cuda(), sc.cuda(), qz.cuda())
+    y = ops.awq_gemm(x.cuda(), packed, bias.cuda()).cpu()
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 511, 512, 1000, M - 1])
+    w = oa.dequantize(qw, qz, sc, G).float()
+    ref = (x[rows].float() @ w).double() + bias.double()
+    assert rel_fro(y[rows], ref.to(torch.float16)) < 1e-2
+    assert torch.isfinite(y.float()).all()
+
+
 # up to 64 tokens: the weight-streaming kernel; above: the tcgen05 kernel that dequantizes the weight
 # tiles in shared memory (K = 416 ends in half a 64-value block, N = 200 in a partial tile, groups of 32)
 @pytest.mark.parametrize("M", [3, 9, 17, 33, 64, 65, 100, 300, 1100])
