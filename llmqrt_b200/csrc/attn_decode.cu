@@ -524,10 +524,12 @@ int launch_decode(const void* q, int64_t qbs, const void* kc, const void* vc, in
     // batch 64 x 1 KV head: 15.0 us unsplit against 14.3 us in three splits, left alone).
     if (max_seqlen <= 2048 && ceil_div(max_seqlen, chunk) == 2 && (int64_t)B * Hkv * 4 >= 3 * (int64_t)sm_count()) chunk *= 2;
   }
-  if (const char* env = getenv("LLMQRT_ATTN_CHUNK")) {                 // experiments: force the chunk
-    const int v = atoi(env);
-    if (v >= 16 && (v & (v - 1)) == 0) chunk = v;
-  }
+  static const int forced_chunk = [] {               // LLMQRT_ATTN_CHUNK=<power of two>: keys per block, for A/B runs
+    const char* env = getenv("LLMQRT_ATTN_CHUNK");
+    const int v = env ? atoi(env) : 0;
+    return (v >= 16 && (v & (v - 1)) == 0) ? v : 0;
+  }();
+  if (forced_chunk) chunk = forced_chunk;
   int max_splits = (int)ceil_div(max_seqlen > 0 ? max_seqlen : 1, chunk);
   while (max_splits > 1 && (size_t)B * Hq * max_splits * (D + 2) * 4 > LLMQRT_WS_PARTIAL_BYTES) {
     chunk *= 2;
