@@ -70,6 +70,7 @@ struct TcParams {
   // Row-parallel output under tensor parallelism: instead of going to `out`, the 16-bit results are
   // stored as the tagged words of the NEXT all-reduce call into the peers' buffers (peer_comm.cuh);
   // the row kernel that consumes the sum then only gathers.
+  int store32;                     // two-CTA kernel: output rows are 32-byte aligned, 256-bit stores may be used
   int comm_on, comm_threads, comm_two_step;
   CommDev comm;
 };
@@ -860,6 +861,14 @@ constexpr uint32_t kPairTmemCols = 2 * kPairBN;
 constexpr int kPairThreads = 64 + 256;                                 // producer warp, MMA warp, eight epilogue warps
 __device__ __forceinline__ void pair_epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
+// 32 bytes from registers to global memory in one instruction (the address must be 32-byte aligned): half
+// the store instructions, and every lane writes a whole 32-byte sector.
+__device__ __forceinline__ void st_global_256(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e,
+                                              uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h) : "memory");
+}
+
 // Tile order: the weight tiles are walked in groups of kPairGroup; inside a group the token tile
 // changes fastest.  The clusters that run at the same time then share a few weight tiles and a few
 // token tiles, and a weight group (8 x 256 rows) stays in L2 until every token tile has used it -- with
@@ -1094,7 +1103,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           if (row_ok) {
             if (wide) {                                // v[0..32): 32-bit outputs
-              if (c + 32 <= ncols) {
+              if (c + 32 <= ncols && prm.store32) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                  st_global_256(orow + c * 4 + 32 * k, v[8 * k], v[8 * k + 1], v[8 * k + 2], v[8 * k + 3], v[8 * k + 4],
+                                v[8 * k + 5], v[8 * k + 6], v[8 * k + 7]);
+              } else if (c + 32 <= ncols) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                   reinterpret_cast<uint4*>(orow + c * 4)[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
@@ -1104,7 +1118,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                   if (c + jj < ncols) reinterpret_cast<uint32_t*>(orow + c * 4)[jj] = v[jj];
               }
             } else {                                   // v[0..16): pairs of 16-bit outputs
-              if (c + 32 <= ncols) {
+              if (c + 32 <= ncols && prm.store32) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k)
+                  st_global_256(orow + c * 2 + 32 * k, v[8 * k], v[8 * k + 1], v[8 * k + 2], v[8 * k + 3], v[8 * k + 4],
+                                v[8 * k + 5], v[8 * k + 6], v[8 * k + 7]);
+              } else if (c + 32 <= ncols) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                   reinterpret_cast<uint4*>(orow + c * 2)[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
@@ -1429,6 +1448,7 @@ int gemm_tc(int kind, const void* A, int64_t lda, const void* W, int64_t ldw, in
       prm.tiles_p = (int)ceil_div(M, (int64_t)(2 * kBM));
       prm.tiles_q = (int)ceil_div(N, (int64_t)kPairBN);
       prm.idesc = tc::instr_desc(c_fmt, fmt_act, fmt_w, 2 * kBM, kPairBN);
+      prm.store32 = ((reinterpret_cast<uintptr_t>(epi.out) & 31) == 0 && (epi.ldo * es) % 32 == 0) ? 1 : 0;
       CUtensorMap tm_a, tm_w;
       if (int rc = make_operand_map(&tm_a, A, elt, M, K, lda, kBM)) return rc;
       if (int rc = make_operand_map(&tm_w, W, elt, N, K, ldw, kPairHalfB)) return rc;
