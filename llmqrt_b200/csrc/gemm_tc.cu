@@ -31,6 +31,10 @@
 // shared memory and leave for global memory as 16-byte vectors that are contiguous across lanes.
 //
 // No multicast anywhere: every CTA fetches its own tiles with plain TMA loads.
+//
+// Two relatives of this kernel live further down: gemm_tc_pair_kernel, the two-CTA (cta_group::2) form
+// for prefill-sized M, and the PUSH instantiation of this one, whose epilogue delivers the output rows of
+// a row-parallel layer straight into the other GPUs' all-reduce buffers.
 #include "gemm_w8a8.cuh"
 #include "peer_comm.cuh"
 #include "tc_primitives.cuh"
