@@ -220,7 +220,7 @@ template <typename T, int U>
 __global__ void __launch_bounds__(1024)
 silu_mul_regs_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ y, int8_t* __restrict__ q,
                      float* __restrict__ scale_f32, int64_t I, int64_t slice) {
-  __shared__ float slot_amax;
+  __shared__ float slot_amax[8];                       // slot r: the maximum found by the cluster's CTA r
   pdl_wait_then_trigger();
   const int cl = gridDim.x, rank = blockIdx.x;
   const int64_t m = blockIdx.y, c0 = (int64_t)rank * slice;
@@ -254,7 +254,20 @@ silu_mul_regs_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ 
   }
   if (q) {
     amax = block_reduce_any<true>(amax);
-    if (cl > 1) amax = cluster_reduce<true>(amax, &slot_amax, cl);
+    if (cl > 1) {
+      // every CTA stores its maximum into its slot in EVERY CTA of the cluster, then ONE cluster barrier
+      // (release / acquire) and each CTA reads its own copy: nobody reads remote memory afterwards, so
+      // there is no second barrier before leaving
+      if (threadIdx.x < cl) {
+        uint32_t remote;
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&slot_amax[rank]);
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)threadIdx.x));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(amax) : "memory");
+      }
+      asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+      amax = 0.f;
+      for (int c = 0; c < cl; ++c) amax = fmaxf(amax, slot_amax[c]);
+    }
     float s = round_to<T>(fmaxf(amax, 1e-5f));
     s = round_to<T>(__fmul_rn(s, 1.0f / 127.0f));
     if (rank == 0 && threadIdx.x == 0) scale_f32[m] = s;
@@ -272,7 +285,6 @@ silu_mul_regs_kernel(const T* __restrict__ gate_up, int64_t ld, T* __restrict__ 
         *reinterpret_cast<uint2*>(q + m * I + c0 + u * 8) = *reinterpret_cast<const uint2*>(o);
       }
     }
-    if (cl > 1) cg::this_cluster().sync();           // nobody leaves while its slot may still be read
   }
 }
 
