@@ -4,6 +4,7 @@ import re
 import subprocess
 import sys
 
+import pytest
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -72,6 +73,25 @@ def test_head_assignment_partitions_heads():
     assert (q, kv) == ([0, 1, 2, 3], [0])
     q, kv = head_assignment(28, 4, 8, 1)
     assert (q, kv) == ([4, 5, 6], [0])
+
+
+def test_gpu_worker_models_divide_among_their_ranks():
+    # the model shapes tests/tp_worker.py builds at each world size must be shardable there (a 4 / 2-head
+    # model cannot be spread over 8 ranks: more ranks per KV head than query heads in its group)
+    from llmqrt_b200.tp import head_assignment
+    src = open(os.path.join(ROOT, "tests", "tp_worker.py")).read()
+    m = re.search(r"num_heads=(\d+),\s*num_kv_heads=(\d+)", src)
+    assert m, "tp_worker.py no longer spells out its 8-rank model"
+    big = (int(m.group(1)), int(m.group(2)))
+    for world, (hq, hkv) in ((2, (4, 2)), (4, (4, 2)), (8, big)):
+        seen = []
+        for r in range(world):
+            q, kv = head_assignment(hq, hkv, world, r)
+            assert q and kv
+            seen += q
+        assert sorted(seen) == list(range(hq))
+    with pytest.raises(ValueError):
+        head_assignment(4, 2, 8, 0)
 
 
 _WORKER = r"""
